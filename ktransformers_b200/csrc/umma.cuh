@@ -118,8 +118,7 @@ __host__ __device__ constexpr uint32_t instr_desc(int c_fmt, int a_fmt, int b_fm
 
 // D[tmem] (+)= A[smem] . B[smem].  Called by ALL lanes of a converged warp with warp-uniform operands; ONE elected lane
 // issues the instruction for the whole CTA.  (Issuing from inside `if (lane == 0)` makes the compiler treat every operand
-// as per-thread: each MMA then costs ~20 SASS instructions — register -> uniform-register moves and an ELECT loop —
-// and a dependent ~100-cycle issue chain; measured in profiles/mla_trace_r02.txt.)  bf16/f16 inputs: K = 16 per instruction.
+// as per-thread: each MMA then sits behind a dependent ~100-cycle issue chain; measured in profiles/mla_trace_r02.txt.)  bf16/f16 inputs: K = 16 per instruction.
 __device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n"
