@@ -348,6 +348,46 @@ int ktb200_mla_absorb_o(const void* attn_latent_dev, const void* w_uv_dev, int n
 int ktb200_mla_kv_write(void* kv_cache, int page_size, const void* ckv, const void* k_pe, const int* page_idx,
                         const int* page_offset, int n_tokens, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Token-major operators for decoders with a 32-bit residual stream and per-sequence state (libktb200_seq.so: seq_ops.cu,
+ * window_attn.cu, plus the router of gate.cu).  `dtype` is KTB200_TYPE_BF16 or KTB200_TYPE_F32: the storage type of
+ * activations, weights and the cache; norms, angles, scores, the residual sum and all reductions are fp32.  One launch serves
+ * a ragged batch: token t belongs to sequence slot[t] at position pos[t].
+ *
+ * ktb200_group_rmsnorm_shift: x_out = x_in + mult * (a + b) when a or b is given (x_out != x_in), h = RMS norm of the row in
+ *   `groups` equal consecutive parts times weight, and with `shift` != NULL  hs_t = h_t + (prev - h_t) * shift  where prev is the
+ *   h of row prev_idx[t] of this launch (>= 0), else state row rd_row[t] (>= 0), else zero; h_t is stored to state row
+ *   wr_row[t] when >= 0 (the caller double-buffers the state rows so that no launch reads a row it writes).
+ * ktb200_latent_prep: proj row = [q latent | kv latent | rotated key part | ...]; writes RMS-normed q latent to cq_out and the
+ *   RMS-normed kv latent + the rotated key part (interleaved pairs over the first rot_dims, angle pos * inv_freq[i]) into the
+ *   paged cache row  page_table[slot][pos / page_size] * page_size + pos % page_size  ([R + rot_dim] per row).
+ * ktb200_latent_window_attn: absorbed latent attention, sliding window (<= 0: none), soft-max sink (NULL: none);
+ *   q [T][H][dim + rot_dim], q_abs [H][T][R], out [H][T][R]; splits > 1 cuts each key range into parts (decode with long
+ *   windows) and needs ktb200_latent_window_attn_workspace bytes.
+ * ktb200_sigmoid_gate_mul: out[t][h*vdim + d] = heads[h][t][d] * sigmoid(gate[t*gate_stride + h*vdim + d]).
+ * ktb200_poly_norm: out = c0 N(z) + c1 N(z^2) + c2 N(z^3) + c3 per row, N(y) = y / sqrt(mean(y^2) + eps).
+ * ktb200_experts_gate_up / _down: dense experts [E][ff][width] / [E][width][ff], ids [T][top] int64 and weights [T][top] as
+ *   ktb200_moe_gate_forward writes them; act [T*top][ff]; out [T][width] fp32.
+ * ------------------------------------------------------------------------------------------ */
+int ktb200_group_rmsnorm_shift(const float* x_in, const void* delta_a, int a_type, const void* delta_b, int b_type, float mult, float* x_out,
+                               const void* weight, int groups, float eps, const void* shift, const int* prev_idx, const int* rd_row,
+                               const int* wr_row, float* state, void* h_out, void* hs_out, int n_tokens, int width, int dtype, void* stream);
+int ktb200_latent_prep(const void* proj, long proj_stride, int q_rank, int kv_rank, int rot_dim, int rot_dims, const double* inv_freq,
+                       const void* q_norm_w, const void* kv_norm_w, float eps, const int* pos, const int* slot, const int* page_table,
+                       int max_pages, int page_size, void* cache, void* cq_out, int n_tokens, int dtype, void* stream);
+size_t ktb200_latent_window_attn_workspace(int n_tokens, int num_heads, int kv_rank, int splits);
+int ktb200_latent_window_attn(const void* q, const void* q_abs, int num_heads, int dim, int rot_dim, int kv_rank, int rot_dims,
+                              const double* inv_freq, float scale, const float* sink, int window, const int* pos, const int* slot,
+                              const int* page_table, int max_pages, int page_size, const void* cache, void* out, int n_tokens, int splits,
+                              void* workspace, int dtype, void* stream);
+int ktb200_sigmoid_gate_mul(const void* heads, const void* gate, long gate_stride, void* out, int n_tokens, int num_heads, int vdim,
+                            int dtype, void* stream);
+int ktb200_poly_norm(const void* z, void* out, const float* coef, float eps, int n_tokens, int ff, int dtype, void* stream);
+int ktb200_experts_gate_up(const void* x, const int64_t* ids, int top, const void* w_gate, const void* w_up, void* act, int n_tokens,
+                           int width, int ff, int dtype, void* stream);
+int ktb200_experts_down(const void* act, const int64_t* ids, const float* weights, int top, const void* w_down, float* out, int n_tokens,
+                        int width, int ff, int dtype, void* stream);
+
 /* Diagnostics (bench.py --probe): time a plain read-only stream over `bytes` of device memory.
  * mode 0 = grid-stride coalesced 16-byte loads; mode 1 = every warp reads chunk_bytes pieces at hashed offsets
  * (the access shape of the expert GEMV).  Establishes the practical read ceiling next to MEASURED_PEAKS' copy figure. */

@@ -1,0 +1,283 @@
+// Token-major operators of decoder layers that keep a 32-bit residual stream and per-sequence state (libktb200_seq.so).
+//
+//   ktb200_group_rmsnorm_shift   x_out = x_in + mult * (a + b)   (optional), then RMS norm in `groups` equal parts, then an
+//                                optional token shift  hs_t = h_t + (h_{t-1} - h_t) * mu  whose h_{t-1} comes from the same
+//                                step (recomputed from the previous row) or from the per-sequence state rows
+//   ktb200_latent_prep           what follows the fused down-projections of latent attention: RMS norm of the query latent,
+//                                RMS norm of the key/value latent, rotation of the shared rotated key part, paged cache write
+//   ktb200_sigmoid_gate_mul      heads [H][T][dv] * sigmoid(gate [T][H*dv]) -> [T][H*dv]
+//   ktb200_poly_norm             a N(z) + b N(z^2) + c N(z^3) + e,  N(y) = y / sqrt(mean(y^2) + eps) over a token's row
+//   ktb200_experts_gate_up/_down per (token, slot) pair GEMVs over dense (bf16 / f32) expert weights: silu(gate) * up, then
+//                                the weighted sum of the chosen experts' down projections in fp32
+//
+// Every kernel is templated on the storage type T (bf16 or float) of activations and weights; norms, angles, the residual
+// sum, sigmoid / silu arguments and all reductions are fp32 (angles: fp64 tables).  Rows are addressed through per-token
+// index arrays, so one launch serves a ragged batch of prompt portions and decode tokens alike.
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+#include "seq_common.cuh"
+
+namespace ktb {
+
+// ------------------------------------------------------------------------------------------------ norm + token shift
+// One CTA per token.  smem: inv[2][groups] | red
+template <typename T>
+__global__ void __launch_bounds__(256) group_norm_shift_kernel(const float* __restrict__ x_in, const void* da, int a_type, const void* db, int b_type, float mult,
+                                                               float* __restrict__ x_out, const T* __restrict__ w, int groups, float eps, const T* __restrict__ mu,
+                                                               const int* __restrict__ prev_idx, const int* __restrict__ rd_row, const int* __restrict__ wr_row,
+                                                               float* __restrict__ state, T* __restrict__ h_out, T* __restrict__ hs_out, int D) {
+    extern __shared__ float sm[];
+    float* inv_cur = sm;
+    float* inv_prev = sm + groups;
+    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
+    const int gs = D / groups;
+    const bool add = da != nullptr || db != nullptr;
+    const int pi = (mu && prev_idx) ? prev_idx[t] : -1;      // row of the previous token inside this step, or -1
+    auto row_val = [&](int r, int i) -> float {
+        float v = x_in[(long)r * D + i];
+        if (add) {
+            float s = 0.f;
+            if (da) s += load_hidden(da, (long)r * D + i, a_type);
+            if (db) s += load_hidden(db, (long)r * D + i, b_type);
+            v = v + mult * s;
+        }
+        return v;
+    };
+    for (int g = warp; g < groups; g += nw) {
+        float sc = 0.f, sp = 0.f;
+        for (int i = lane; i < gs; i += 32) {
+            const float v = row_val(t, g * gs + i);
+            sc += v * v;
+            if (pi >= 0) {
+                const float u = row_val(pi, g * gs + i);
+                sp += u * u;
+            }
+        }
+        sc = warp_sum(sc);
+        sp = warp_sum(sp);
+        if (lane == 0) {
+            inv_cur[g] = 1.0f / sqrtf(sc / (float)gs + eps);
+            inv_prev[g] = 1.0f / sqrtf(sp / (float)gs + eps);
+        }
+    }
+    __syncthreads();
+    const int rr = (mu && rd_row) ? rd_row[t] : -1;
+    const int wr = (mu && wr_row) ? wr_row[t] : -1;
+    for (int i = tid; i < D; i += blockDim.x) {
+        const float v = row_val(t, i);
+        if (add && x_out) x_out[(long)t * D + i] = v;
+        const float wi = to_f(w[i]);
+        const float h = v * inv_cur[i / gs] * wi;
+        if (h_out) h_out[(long)t * D + i] = from_f<T>(h);
+        if (mu) {
+            float hp = 0.f;
+            if (pi >= 0) hp = row_val(pi, i) * inv_prev[i / gs] * wi;
+            else if (rr >= 0) hp = state[(long)rr * D + i];
+            if (hs_out) hs_out[(long)t * D + i] = from_f<T>(h + (hp - h) * to_f(mu[i]));
+            if (wr >= 0) state[(long)wr * D + i] = h;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ latent prep
+// One CTA per token.  proj row = [ q latent (q_rank) | kv latent (kv_rank) | rotated key part (rot_dim) | ... ].
+template <typename T>
+__global__ void __launch_bounds__(256) latent_prep_kernel(const T* __restrict__ proj, long proj_stride, int q_rank, int kv_rank, int rot_dim, int rot_dims,
+                                                          const double* __restrict__ inv_freq, const T* __restrict__ qn_w, const T* __restrict__ kvn_w, float eps,
+                                                          const int* __restrict__ pos, const int* __restrict__ slot, const int* __restrict__ page_table, int max_pages,
+                                                          int page_size, T* __restrict__ cache, T* __restrict__ cq_out) {
+    __shared__ float red[32];
+    const int t = blockIdx.x, tid = threadIdx.x;
+    const T* p = proj + (long)t * proj_stride;
+    float sq = 0.f, sk = 0.f;
+    for (int i = tid; i < q_rank; i += blockDim.x) { const float v = to_f(p[i]); sq += v * v; }
+    for (int i = tid; i < kv_rank; i += blockDim.x) { const float v = to_f(p[q_rank + i]); sk += v * v; }
+    sq = block_sum(sq, red);
+    sk = block_sum(sk, red);
+    const float iq = q_rank ? 1.0f / sqrtf(sq / (float)q_rank + eps) : 0.f;
+    const float ik = 1.0f / sqrtf(sk / (float)kv_rank + eps);
+    for (int i = tid; i < q_rank; i += blockDim.x) cq_out[(long)t * q_rank + i] = from_f<T>(to_f(p[i]) * iq * to_f(qn_w[i]));
+    const int ps = pos[t];
+    const long row = (long)page_table[(long)slot[t] * max_pages + ps / page_size] * page_size + ps % page_size;
+    T* c = cache + row * (kv_rank + rot_dim);
+    for (int i = tid; i < kv_rank; i += blockDim.x) c[i] = from_f<T>(to_f(p[q_rank + i]) * ik * to_f(kvn_w[i]));
+    const T* kr = p + q_rank + kv_rank;
+    for (int i = tid; i < rot_dim; i += blockDim.x) {
+        float v = to_f(kr[i]);
+        if (i < rot_dims) {
+            double sn, cs;
+            sincos((double)ps * inv_freq[i >> 1], &sn, &cs);
+            const float other = to_f(kr[i ^ 1]);
+            v = (i & 1) ? v * (float)cs + other * (float)sn : v * (float)cs - other * (float)sn;
+        }
+        c[kv_rank + i] = from_f<T>(v);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ output gate
+template <typename T>
+__global__ void sigmoid_gate_mul_kernel(const T* __restrict__ heads, const T* __restrict__ gate, long gate_stride, T* __restrict__ out, int n_tokens, int H, int dv) {
+    const long n = (long)n_tokens * H * dv;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+        const int d = (int)(i % dv);
+        const int h = (int)((i / dv) % H);
+        const long t = i / ((long)dv * H);
+        const float o = to_f(heads[((long)h * n_tokens + t) * dv + d]);
+        const float g = to_f(gate[t * gate_stride + (long)h * dv + d]);
+        out[i] = from_f<T>(o * (1.0f / (1.0f + expf(-g))));
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ PolyNorm
+template <typename T>
+__global__ void __launch_bounds__(256) poly_norm_kernel(const T* __restrict__ z, T* __restrict__ out, const float* __restrict__ coef, float eps, int F) {
+    __shared__ float red[32];
+    const long t = blockIdx.x;
+    const T* zr = z + t * F;
+    float s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    for (int i = threadIdx.x; i < F; i += blockDim.x) {
+        const float v = to_f(zr[i]), v2 = v * v, v3 = v2 * v;
+        s1 += v2; s2 += v2 * v2; s3 += v3 * v3;
+    }
+    s1 = block_sum(s1, red); s2 = block_sum(s2, red); s3 = block_sum(s3, red);
+    const float a = coef[0] / sqrtf(s1 / (float)F + eps), b = coef[1] / sqrtf(s2 / (float)F + eps), c = coef[2] / sqrtf(s3 / (float)F + eps), e = coef[3];
+    for (int i = threadIdx.x; i < F; i += blockDim.x) {
+        const float v = to_f(zr[i]);
+        out[t * F + i] = from_f<T>(a * v + b * v * v + c * v * v * v + e);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ dense experts, per pair
+// grid (pairs, row blocks); a warp owns ff rows r = blockIdx.y * nw + warp (+ stride); the token's row sits in shared memory.
+template <typename T>
+__global__ void __launch_bounds__(256) experts_gate_up_kernel(const T* __restrict__ x, const int64_t* __restrict__ ids, int top, const T* __restrict__ Wg, const T* __restrict__ Wu,
+                                                              T* __restrict__ act, int D, int F) {
+    extern __shared__ float xs[];
+    const long p = blockIdx.x;
+    const long t = p / top;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) xs[i] = to_f(x[t * D + i]);
+    __syncthreads();
+    const long e = ids[p];
+    const T* g = Wg + e * (long)F * D;
+    const T* u = Wu + e * (long)F * D;
+    for (int r = blockIdx.y * nw + warp; r < F; r += gridDim.y * nw) {
+        float sg = 0.f, su = 0.f;
+        for (int i = lane; i < D; i += 32) {
+            sg += to_f(g[(long)r * D + i]) * xs[i];
+            su += to_f(u[(long)r * D + i]) * xs[i];
+        }
+        sg = warp_sum(sg);
+        su = warp_sum(su);
+        if (lane == 0) act[p * F + r] = from_f<T>(act_silu(sg) * su);
+    }
+}
+
+// grid (tokens, row blocks); out[t][d] = sum_j w[t][j] * Wd[ids[t][j]][d] . act[t*top + j]   (fp32, slot order)
+template <typename T>
+__global__ void __launch_bounds__(256) experts_down_kernel(const T* __restrict__ act, const int64_t* __restrict__ ids, const float* __restrict__ wts, int top,
+                                                           const T* __restrict__ Wd, float* __restrict__ out, int D, int F) {
+    extern __shared__ float as[];   // [top][F]
+    const long t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    for (int i = threadIdx.x; i < top * F; i += blockDim.x) as[i] = to_f(act[t * top * F + i]);
+    __syncthreads();
+    for (int d = blockIdx.y * nw + warp; d < D; d += gridDim.y * nw) {
+        float acc = 0.f;
+        for (int j = 0; j < top; j++) {
+            const T* wd = Wd + (ids[t * top + j] * (long)D + d) * F;
+            float s = 0.f;
+            for (int i = lane; i < F; i += 32) s += to_f(wd[i]) * as[j * F + i];
+            s = warp_sum(s);
+            acc = fmaf(wts[t * top + j], s, acc);
+        }
+        if (lane == 0) out[t * D + d] = acc;
+    }
+}
+
+}  // namespace ktb
+
+using namespace ktb;
+
+#define SEQ_DISPATCH(dtype, ...)                                                           \
+    do {                                                                                   \
+        if ((dtype) == KTB200_TYPE_BF16) { using T = __nv_bfloat16; __VA_ARGS__; }         \
+        else if ((dtype) == KTB200_TYPE_F32) { using T = float; __VA_ARGS__; }             \
+        else { set_error("dtype must be bf16 or f32"); return KTB200_EINVAL; }             \
+    } while (0)
+
+extern "C" int ktb200_group_rmsnorm_shift(const float* x_in, const void* delta_a, int a_type, const void* delta_b, int b_type, float mult, float* x_out,
+                                          const void* weight, int groups, float eps, const void* shift, const int* prev_idx, const int* rd_row, const int* wr_row,
+                                          float* state, void* h_out, void* hs_out, int n_tokens, int width, int dtype, void* stream) {
+    if (!x_in || !weight || groups <= 0 || width <= 0 || width % groups || n_tokens < 0) { set_error("group_rmsnorm_shift: bad argument"); return KTB200_EINVAL; }
+    if ((delta_a || delta_b) && (!x_out || x_out == x_in)) { set_error("group_rmsnorm_shift: the sum needs a separate output row buffer"); return KTB200_EINVAL; }
+    if (shift && (!prev_idx || !rd_row || !wr_row || !state || !hs_out)) { set_error("group_rmsnorm_shift: shift needs its index rows, state and output"); return KTB200_EINVAL; }
+    if (n_tokens == 0) return KTB200_OK;
+    const size_t smem = 2 * (size_t)groups * sizeof(float);
+    SEQ_DISPATCH(dtype, (group_norm_shift_kernel<T><<<n_tokens, 256, smem, (cudaStream_t)stream>>>(x_in, delta_a, a_type, delta_b, b_type, mult, x_out, (const T*)weight, groups, eps,
+                                                                                                   (const T*)shift, prev_idx, rd_row, wr_row, state, (T*)h_out, (T*)hs_out, width)));
+    KTB_LAUNCH_CHECK();
+    return KTB200_OK;
+}
+
+extern "C" int ktb200_latent_prep(const void* proj, long proj_stride, int q_rank, int kv_rank, int rot_dim, int rot_dims, const double* inv_freq, const void* q_norm_w,
+                                  const void* kv_norm_w, float eps, const int* pos, const int* slot, const int* page_table, int max_pages, int page_size, void* cache,
+                                  void* cq_out, int n_tokens, int dtype, void* stream) {
+    if (!proj || !kv_norm_w || !pos || !slot || !page_table || !cache || kv_rank <= 0 || rot_dim < 0 || rot_dims < 0 || rot_dims > rot_dim || (rot_dims & 1) || q_rank < 0 ||
+        (q_rank && (!q_norm_w || !cq_out)) || (rot_dims && !inv_freq) || page_size <= 0 || max_pages <= 0) {
+        set_error("latent_prep: bad argument");
+        return KTB200_EINVAL;
+    }
+    if (n_tokens <= 0) return KTB200_OK;
+    SEQ_DISPATCH(dtype, (latent_prep_kernel<T><<<n_tokens, 256, 0, (cudaStream_t)stream>>>((const T*)proj, proj_stride, q_rank, kv_rank, rot_dim, rot_dims, inv_freq, (const T*)q_norm_w,
+                                                                                           (const T*)kv_norm_w, eps, pos, slot, page_table, max_pages, page_size, (T*)cache, (T*)cq_out)));
+    KTB_LAUNCH_CHECK();
+    return KTB200_OK;
+}
+
+extern "C" int ktb200_sigmoid_gate_mul(const void* heads, const void* gate, long gate_stride, void* out, int n_tokens, int num_heads, int vdim, int dtype, void* stream) {
+    if (!heads || !gate || !out || num_heads <= 0 || vdim <= 0) { set_error("sigmoid_gate_mul: bad argument"); return KTB200_EINVAL; }
+    if (n_tokens <= 0) return KTB200_OK;
+    const long n = (long)n_tokens * num_heads * vdim;
+    const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+    SEQ_DISPATCH(dtype, (sigmoid_gate_mul_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>((const T*)heads, (const T*)gate, gate_stride, (T*)out, n_tokens, num_heads, vdim)));
+    KTB_LAUNCH_CHECK();
+    return KTB200_OK;
+}
+
+extern "C" int ktb200_poly_norm(const void* z, void* out, const float* coef, float eps, int n_tokens, int ff, int dtype, void* stream) {
+    if (!z || !out || !coef || ff <= 0) { set_error("poly_norm: bad argument"); return KTB200_EINVAL; }
+    if (n_tokens <= 0) return KTB200_OK;
+    SEQ_DISPATCH(dtype, (poly_norm_kernel<T><<<n_tokens, 256, 0, (cudaStream_t)stream>>>((const T*)z, (T*)out, coef, eps, ff)));
+    KTB_LAUNCH_CHECK();
+    return KTB200_OK;
+}
+
+extern "C" int ktb200_experts_gate_up(const void* x, const int64_t* ids, int top, const void* w_gate, const void* w_up, void* act, int n_tokens, int width, int ff, int dtype,
+                                      void* stream) {
+    if (!x || !ids || !w_gate || !w_up || !act || top <= 0 || width <= 0 || ff <= 0 || width * sizeof(float) > 200 * 1024) { set_error("experts_gate_up: bad argument"); return KTB200_EINVAL; }
+    if (n_tokens <= 0) return KTB200_OK;
+    const size_t smem = (size_t)width * sizeof(float);
+    const int ry = (ff + 7) / 8 < 16 ? (ff + 7) / 8 : 16;
+    SEQ_DISPATCH(dtype, {
+        if (smem > 48 * 1024) KTB_CUDA_CHECK(cudaFuncSetAttribute(experts_gate_up_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        experts_gate_up_kernel<T><<<dim3(n_tokens * top, ry), 256, smem, (cudaStream_t)stream>>>((const T*)x, ids, top, (const T*)w_gate, (const T*)w_up, (T*)act, width, ff);
+    });
+    KTB_LAUNCH_CHECK();
+    return KTB200_OK;
+}
+
+extern "C" int ktb200_experts_down(const void* act, const int64_t* ids, const float* weights, int top, const void* w_down, float* out, int n_tokens, int width, int ff, int dtype,
+                                   void* stream) {
+    if (!act || !ids || !weights || !w_down || !out || top <= 0 || width <= 0 || ff <= 0 || (size_t)top * ff * sizeof(float) > 200 * 1024) { set_error("experts_down: bad argument"); return KTB200_EINVAL; }
+    if (n_tokens <= 0) return KTB200_OK;
+    const size_t smem = (size_t)top * ff * sizeof(float);
+    const int ry = (width + 7) / 8 < 16 ? (width + 7) / 8 : 16;
+    SEQ_DISPATCH(dtype, {
+        if (smem > 48 * 1024) KTB_CUDA_CHECK(cudaFuncSetAttribute(experts_down_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        experts_down_kernel<T><<<dim3(n_tokens, ry), 256, smem, (cudaStream_t)stream>>>((const T*)act, ids, weights, top, (const T*)w_down, out, width, ff);
+    });
+    KTB_LAUNCH_CHECK();
+    return KTB200_OK;
+}

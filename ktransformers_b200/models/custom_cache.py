@@ -67,3 +67,149 @@ class StaticCache:
         for t in self.key_cache:
             t.zero_()
         self.past_tokens = [0] * len(self.past_tokens)
+
+
+class ForwardBatch:
+    """One step's ragged batch, flattened token-major: what the scheduler hands to a model's step function.
+
+    `tokens`, `pos`, `slot` [T]; for layers that keep a previous-token row: `prev_idx` (row of the previous token inside this
+    step or -1), `rd_row` / `wr_row` (state rows to read when the previous token came in an earlier step / to write for the
+    last token of a sequence's portion; -1: none).  `want` [W]: rows whose logits the caller asked for."""
+
+    __slots__ = ("tokens", "pos", "slot", "prev_idx", "rd_row", "wr_row", "want", "n_tokens", "max_kv")
+
+    def __init__(self, meta: torch.Tensor, tokens: torch.Tensor, want: torch.Tensor, max_kv: int):
+        self.pos, self.slot, self.prev_idx, self.rd_row, self.wr_row = meta[0], meta[1], meta[2], meta[3], meta[4]
+        self.tokens, self.want, self.n_tokens, self.max_kv = tokens, want, int(tokens.shape[0]), max_kv
+
+
+class PagedStateCache:
+    """Pages of per-token cache rows plus fixed-size per-sequence state rows, for models whose layers keep a (windowed) latent
+    cache and a previous-token row.
+
+    * One pool of `num_pages` pages of `page_size` tokens; layer l's buffer is `[num_pages, page_size, row_widths[l]]` and all
+      layers share the page ids, so a sequence has ONE page table row (`page_table[slot]`, device int32).
+    * A sequence occupies a slot from `open()` to `close()`; `extend(slot, n)` reserves pages for the next n tokens and returns
+      the first position; pages that fall wholly behind `window` (the largest look-back of any layer) are given back while the
+      sequence is still running, and pages and slots are reused without being cleared: readers never look outside
+      `[pos - window + 1, pos]`, and position 0 reads no state.
+    * State rows are double-buffered per slot (`state[l]` is `[2 * max_slots, width]` fp32): a step reads row `2*slot + parity`
+      and writes row `2*slot + 1 - parity`, then `commit()` flips the parity of the slots it touched, so no kernel launch
+      reads a row it also writes.
+
+    The reference's StaticCache (archive/ktransformers/models/custom_cache.py:26-200) keeps a static identity page table per
+    batch row; this manager adds allocation, release and the recurrent rows."""
+
+    def __init__(self, row_widths, state_width: int, max_tokens: int, max_slots: int, device, dtype=torch.bfloat16, page_size: int = 64,
+                 window: Optional[int] = None):
+        self.device, self.dtype, self.page_size, self.window = torch.device(device), dtype, int(page_size), window
+        self.max_slots = int(max_slots)
+        # every live sequence may hold one partly filled page at each end of its range
+        self.num_pages = (int(max_tokens) + page_size - 1) // page_size + 2 * self.max_slots
+        self.max_pages_per_seq = (int(max_tokens) + page_size - 1) // page_size + 2
+        self.key_cache = [torch.zeros((self.num_pages, page_size, int(w)), dtype=dtype, device=device) for w in row_widths]
+        self.state = [torch.zeros((2 * self.max_slots, int(state_width)), dtype=torch.float32, device=device) for _ in row_widths]
+        self.page_table = torch.zeros((self.max_slots, self.max_pages_per_seq), dtype=torch.int32, device=device)
+        self._table_host = torch.zeros((self.max_slots, self.max_pages_per_seq), dtype=torch.int32)
+        self._free_pages = list(range(self.num_pages - 1, -1, -1))
+        self._free_slots = list(range(self.max_slots - 1, -1, -1))
+        self._slot_of: Dict[Any, int] = {}
+        self._len = [0] * self.max_slots            # tokens written so far
+        self._first_page = [0] * self.max_slots     # logical pages below this index were given back
+        self._parity = [0] * self.max_slots
+        self._touched: set = set()
+        self._dirty = False
+
+    # -- sequences ---------------------------------------------------------------------------------
+    def open(self, seq_id) -> int:
+        if seq_id in self._slot_of:
+            return self._slot_of[seq_id]
+        if not self._free_slots:
+            raise MemoryError("PagedStateCache: no free sequence slot")
+        s = self._free_slots.pop()
+        self._slot_of[seq_id] = s
+        self._len[s], self._first_page[s], self._parity[s] = 0, 0, 0
+        return s
+
+    def close(self, seq_id) -> None:
+        s = self._slot_of.pop(seq_id)
+        n_pages = (self._len[s] + self.page_size - 1) // self.page_size
+        for lp in range(self._first_page[s], n_pages):
+            self._free_pages.append(int(self._table_host[s, lp]))
+        self._len[s] = 0
+        self._free_slots.append(s)
+
+    def slot(self, seq_id) -> int:
+        return self._slot_of[seq_id]
+
+    def length(self, seq_id) -> int:
+        return self._len[self._slot_of[seq_id]]
+
+    def free_tokens(self) -> int:
+        return len(self._free_pages) * self.page_size
+
+    # -- pages -------------------------------------------------------------------------------------
+    def extend(self, slot: int, n: int) -> int:
+        """Reserve pages for positions [len, len + n); returns len."""
+        start = self._len[slot]
+        have = (start + self.page_size - 1) // self.page_size
+        need = (start + n + self.page_size - 1) // self.page_size
+        if need > self.max_pages_per_seq:
+            raise MemoryError("PagedStateCache: sequence longer than the page table")
+        if need - have > len(self._free_pages):
+            raise MemoryError("PagedStateCache: out of pages")
+        for lp in range(have, need):
+            self._table_host[slot, lp] = self._free_pages.pop()
+            self._dirty = True
+        self._len[slot] = start + n
+        self._touched.add(slot)
+        return start
+
+    def release_behind(self, slot: int) -> None:
+        """Give back the pages that no later token of this sequence can look at."""
+        if self.window is None:
+            return
+        keep_from = max(0, self._len[slot] - (self.window - 1)) // self.page_size   # first page the NEXT token may read
+        for lp in range(self._first_page[slot], keep_from):
+            self._free_pages.append(int(self._table_host[slot, lp]))
+        self._first_page[slot] = max(self._first_page[slot], keep_from)
+
+    def sync_table(self) -> torch.Tensor:
+        if self._dirty:
+            self.page_table.copy_(self._table_host, non_blocking=False)
+            self._dirty = False
+        return self.page_table
+
+    # -- state rows --------------------------------------------------------------------------------
+    def state_rows(self, slot: int, start: int):
+        """(row to read or -1 when the portion starts the sequence, row to write)"""
+        p = self._parity[slot]
+        return (2 * slot + p if start > 0 else -1), 2 * slot + 1 - p
+
+    def commit(self) -> None:
+        for s in self._touched:
+            self._parity[s] ^= 1
+            self.release_behind(s)
+        self._touched.clear()
+
+    def build_batch(self, entries, want_all: bool = False) -> ForwardBatch:
+        """entries: [(seq_id, tokens, want)] — reserve pages, lay out the per-token index rows, one host-to-device copy."""
+        rows, toks, want, base, max_kv = [[], [], [], [], []], [], [], 0, 0
+        for seq_id, tokens, w in entries:
+            s = self.open(seq_id)
+            n = len(tokens)
+            start = self.extend(s, n)
+            rd, wr = self.state_rows(s, start)
+            rows[0] += range(start, start + n)
+            rows[1] += [s] * n
+            rows[2] += [-1] + list(range(base, base + n - 1))
+            rows[3] += [rd] + [-1] * (n - 1)
+            rows[4] += [-1] * (n - 1) + [wr]
+            toks += tokens
+            want += [base + i for i in (range(n) if want_all else w)]
+            base += n
+            max_kv = max(max_kv, start + n)
+        self.sync_table()
+        meta = torch.tensor(rows, dtype=torch.int32).to(self.device, non_blocking=True)
+        return ForwardBatch(meta, torch.tensor(toks, dtype=torch.int64).to(self.device, non_blocking=True),
+                            torch.tensor(want, dtype=torch.int64).to(self.device, non_blocking=True), max_kv)

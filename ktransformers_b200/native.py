@@ -101,6 +101,25 @@ SYMBOLS = {
 }
 
 
+# libktb200_seq.so: the token-major operators (csrc/seq_ops.cu, csrc/window_attn.cu) + the router (csrc/gate.cu)
+_F, _D = C.c_float, C.POINTER(C.c_double)
+SEQ_SYMBOLS = {
+    "ktb200_last_error": (C.c_char_p, []),
+    "ktb200_launch_count": (C.c_ulonglong, []),
+    "ktb200_moe_gate_forward": (_I, [C.POINTER(GateConfig), _I, _VP, _VP, _VP, _VP, _VP, _VP]),
+    "ktb200_group_rmsnorm_shift": (_I, [_VP, _VP, _I, _VP, _I, _F, _VP, _VP, _I, _F, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _VP]),
+    "ktb200_latent_prep": (_I, [_VP, _L, _I, _I, _I, _I, _VP, _VP, _VP, _F, _VP, _VP, _VP, _I, _I, _VP, _VP, _I, _I, _VP]),
+    "ktb200_latent_window_attn_workspace": (C.c_size_t, [_I, _I, _I, _I]),
+    "ktb200_latent_window_attn": (_I, [_VP, _VP, _I, _I, _I, _I, _I, _VP, _F, _VP, _I, _VP, _VP, _VP, _I, _I, _VP, _VP, _I, _I, _VP, _I, _VP]),
+    "ktb200_sigmoid_gate_mul": (_I, [_VP, _VP, _L, _VP, _I, _I, _I, _I, _VP]),
+    "ktb200_poly_norm": (_I, [_VP, _VP, _VP, _F, _I, _I, _I, _VP]),
+    "ktb200_experts_gate_up": (_I, [_VP, _VP, _I, _VP, _VP, _VP, _I, _I, _I, _I, _VP]),
+    "ktb200_experts_down": (_I, [_VP, _VP, _VP, _I, _VP, _VP, _I, _I, _I, _I, _VP]),
+}
+SEQ_LIB_PATH = os.path.join(_HERE, "libktb200_seq.so")
+_seq_lib = None
+
+
 class EpComm(C.Structure):
     """ktb200_ep_comm (include/ktb200.h): peer-mapped token / partial / flag buffers of an expert-parallel group."""
     _fields_ = [("rank", C.c_int), ("world", C.c_int), ("hidden_size", C.c_int), ("hidden_type", C.c_int),
@@ -139,6 +158,47 @@ def lib() -> C.CDLL:
                     fn.argtypes = args
                 _lib = l
     return _lib
+
+
+def build_seq(verbose: bool = False) -> str:
+    """Compile libktb200_seq.so alone (four small sources, seconds).  Serialised across processes by a lock file."""
+    import fcntl
+    out = None if verbose else subprocess.DEVNULL
+    os.makedirs(os.path.join(CSRC, "build"), exist_ok=True)
+    with open(os.path.join(CSRC, "build", ".seq.lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        subprocess.check_call(["make", "-C", CSRC, "-j", "4", "seq"], stdout=out)
+    return SEQ_LIB_PATH
+
+
+def seq_lib(build_if_missing: bool = True) -> C.CDLL:
+    """The token-major operator library.  A fresh checkout compiles it on first use (it is all a model of that kind needs);
+    there is no fallback when that fails."""
+    global _seq_lib
+    if _seq_lib is None:
+        with _lock:
+            if _seq_lib is None:
+                if not os.path.exists(SEQ_LIB_PATH):
+                    if not build_if_missing:
+                        raise RuntimeError(f"{SEQ_LIB_PATH} is missing: build it with `make -C ktransformers_b200/csrc seq`")
+                    build_seq()
+                l = C.CDLL(SEQ_LIB_PATH)
+                for name, (res, args) in SEQ_SYMBOLS.items():
+                    fn = getattr(l, name)
+                    fn.restype = res
+                    fn.argtypes = args
+                _seq_lib = l
+    return _seq_lib
+
+
+def check_seq(rc: int) -> None:
+    """`check` for calls into libktb200_seq.so (each library keeps its own last-error text)."""
+    if rc == OK:
+        return
+    msg = seq_lib().ktb200_last_error().decode(errors="replace")
+    if rc == EINVAL:
+        raise ValueError(msg)
+    raise KTB200Error(msg)
 
 
 class KTB200Error(RuntimeError):

@@ -92,3 +92,81 @@ class KDeepseekV2Attention(BaseInjectedModule, DeepseekV3Attention):
             attn = torch.matmul(attn.transpose(1, 2), out_absorb.mT).transpose(1, 2).contiguous()     # [b, 1, h, 128]
         attn = self.o_proj(attn.reshape(bsz, q_len, self.num_heads * self.v_head_dim))
         return attn, None, past_key_value
+
+
+class KLatentWindowAttention(torch.nn.Module):
+    """Latent attention with a low-rank query, a sliding window, a soft-max sink and a sigmoid output gate, run absorbed over
+    the paged latent cache — the same formulation KDeepseekV2Attention uses for decode, here for prompt portions as well.
+
+        P        = [W_dq ; W_dkv ; W_g] hs                      one GEMM over the three matrices that read the mixer input
+        cq, c, k_r -> cache                                      ktb200_latent_prep (two RMS norms, rotation, paged write)
+        q        = W_uq cq                                       GEMM
+        qa_h     = W_uk,h^T q_h[:dim]                            batched GEMM (absorb)
+        lat_h    = sum_j softmax_sink(qa_h . c_j + rot(q_h[dim:]) . k_r,j) c_j     ktb200_latent_window_attn
+        o_h      = W_uv,h lat_h                                  batched GEMM (absorb)
+        out      = W_o (o * sigmoid(g))                          ktb200_sigmoid_gate_mul + GEMM
+
+    Only c and k_r are cached (`kv_rank + rot_dim` values per token and layer).  Sizes, window, sink, scale and the rotation
+    constants are constructor parameters (models/configuration_lekapel.LatentAttentionSpec)."""
+
+    def __init__(self, width: int, spec, eps: float, layer_idx: int, dtype=torch.bfloat16, device="cuda"):
+        super().__init__()
+        P = lambda *shape, dt=dtype: torch.nn.Parameter(torch.empty(shape, dtype=dt, device=device), requires_grad=False)
+        s = self.spec = spec
+        self.width, self.eps, self.layer_idx = width, eps, layer_idx
+        self.n_in = s.q_rank + s.kv_rank + s.rot_dim + s.heads * s.vdim
+        self.w_in = P(self.n_in, width)
+        self.q_norm, self.kv_norm = P(s.q_rank), P(s.kv_rank)
+        self.uq = P(s.heads * (s.dim + s.rot_dim), s.q_rank)
+        self.w_uk = P(s.heads, s.dim, s.kv_rank)
+        self.w_uv_t = P(s.heads, s.kv_rank, s.vdim)
+        self.sink = P(s.heads, dt=torch.float32)
+        self.o = P(width, s.heads * s.vdim)
+        i = torch.arange(s.rot.dims // 2, dtype=torch.float64)
+        self.register_buffer("inv_freq", (float(s.rot.base) ** (-2.0 * i / max(s.rot.dims, 1))).to(device), persistent=False)
+
+    def load(self, loader, prefix: str):
+        s, t = self.spec, lambda n: loader.load_tensor(prefix + n, "cpu")
+        self.w_in.data.copy_(torch.cat([t("dq"), t("dkv"), t("g")], 0))
+        self.q_norm.data.copy_(t("dq.norm"))
+        self.kv_norm.data.copy_(t("dkv.norm"))
+        self.uq.data.copy_(t("uq"))
+        self.w_uk.data.copy_(t("uk").view(s.heads, s.dim, s.kv_rank))
+        self.w_uv_t.data.copy_(t("uv").view(s.heads, s.vdim, s.kv_rank).transpose(1, 2))
+        self.sink.data.copy_(t("sink").float())
+        self.o.data.copy_(t("o"))
+
+    def pick_splits(self, n_tokens: int, max_kv: int) -> int:
+        """Cut the key range when a small batch would leave most SMs idle on a long window."""
+        s = self.spec
+        keys = min(s.window, max_kv) if s.window else max_kv
+        ctas = n_tokens * ((s.heads + 7) // 8)
+        if ctas >= 148 or keys <= 256:
+            return 1
+        return max(1, min(32, keys // 128, 296 // ctas))
+
+    def forward(self, hs: torch.Tensor, batch, cache) -> torch.Tensor:
+        s, T, dev, dt = self.spec, hs.shape[0], hs.device, hs.dtype
+        lib, code, st = native.seq_lib(), native.GGML_BF16 if dt == torch.bfloat16 else native.GGML_F32, torch.cuda.current_stream(hs.device).cuda_stream
+        kv = cache.key_cache[self.layer_idx]
+        proj = torch.nn.functional.linear(hs, self.w_in)
+        cq = torch.empty((T, s.q_rank), dtype=dt, device=dev)
+        native.check_seq(lib.ktb200_latent_prep(proj.data_ptr(), self.n_in, s.q_rank, s.kv_rank, s.rot_dim, s.rot.dims, self.inv_freq.data_ptr(), self.q_norm.data_ptr(),
+                                                self.kv_norm.data_ptr(), float(self.eps), batch.pos.data_ptr(), batch.slot.data_ptr(), cache.page_table.data_ptr(),
+                                                cache.max_pages_per_seq, cache.page_size, kv.data_ptr(), cq.data_ptr(), T, code, st))
+        q = torch.nn.functional.linear(cq, self.uq)
+        if s.dim:
+            q_abs = torch.bmm(q.view(T, s.heads, s.dim + s.rot_dim)[:, :, : s.dim].transpose(0, 1), self.w_uk)
+        else:
+            q_abs = torch.zeros((s.heads, T, s.kv_rank), dtype=dt, device=dev)
+        lat = torch.empty((s.heads, T, s.kv_rank), dtype=dt, device=dev)
+        splits = self.pick_splits(T, batch.max_kv)
+        ws = torch.empty(lib.ktb200_latent_window_attn_workspace(T, s.heads, s.kv_rank, splits) // 4, dtype=torch.float32, device=dev) if splits > 1 else None
+        native.check_seq(lib.ktb200_latent_window_attn(q.data_ptr(), q_abs.data_ptr(), s.heads, s.dim, s.rot_dim, s.kv_rank, s.rot.dims, self.inv_freq.data_ptr(), float(s.scale),
+                                                       self.sink.data_ptr(), s.window or 0, batch.pos.data_ptr(), batch.slot.data_ptr(), cache.page_table.data_ptr(),
+                                                       cache.max_pages_per_seq, cache.page_size, kv.data_ptr(), lat.data_ptr(), T, splits,
+                                                       ws.data_ptr() if ws is not None else None, code, st))
+        o = torch.bmm(lat, self.w_uv_t)
+        og = torch.empty((T, s.heads * s.vdim), dtype=dt, device=dev)
+        native.check_seq(lib.ktb200_sigmoid_gate_mul(o.data_ptr(), proj[:, s.q_rank + s.kv_rank + s.rot_dim:].data_ptr(), self.n_in, og.data_ptr(), T, s.heads, s.vdim, code, st))
+        return torch.nn.functional.linear(og, self.o)

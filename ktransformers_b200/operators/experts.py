@@ -522,3 +522,53 @@ class KDeepseekV3MoEV2(_KDeepseekMoEMixin, BaseInjectedModule, _V3):
         if self.config.n_shared_experts is not None:
             y = y + self.shared_experts(identity).view(*orig_shape)
         return y
+
+
+class KExpertsDense(nn.Module):
+    """Un-quantised (bf16 / fp32) gated-SiLU experts, stacked `[E, ff, width]` / `[E, width, ff]` in HBM, run by the per-pair
+    kernels `ktb200_experts_gate_up` / `ktb200_experts_down` (csrc/seq_ops.cu): every (token, slot) pair is a GEMV pair over its
+    expert's rows, silu(gate) * up in fp32 with one rounding, the weighted sum over a token's slots in fp32 in slot order.
+    The counterpart of KExpertsB200 for checkpoints that ship dense experts (the reference's KExpertsTorch, experts.py:562-678,
+    loops over experts in torch)."""
+
+    def __init__(self, width: int, ff: int, experts: int, dtype=torch.bfloat16, device="cuda"):
+        super().__init__()
+        self.width, self.ff, self.experts = width, ff, experts
+        self.gate = nn.Parameter(torch.empty((experts, ff, width), dtype=dtype, device=device), requires_grad=False)
+        self.up = nn.Parameter(torch.empty((experts, ff, width), dtype=dtype, device=device), requires_grad=False)
+        self.down = nn.Parameter(torch.empty((experts, width, ff), dtype=dtype, device=device), requires_grad=False)
+
+    def load(self, loader, prefix: str, names=("gate", "up", "down")):
+        for e in range(self.experts):
+            for p, n in zip((self.gate, self.up, self.down), names):
+                p.data[e].copy_(loader.load_tensor(f"{prefix}e{e}.{n}", "cpu"))
+
+    def forward(self, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+        """x [T, width], ids [T, top] int64, weights [T, top] fp32 -> [T, width] fp32"""
+        T, top = ids.shape
+        act = torch.empty((T * top, self.ff), dtype=x.dtype, device=x.device)
+        out = torch.empty((T, self.width), dtype=torch.float32, device=x.device)
+        lib, dt, st = native.seq_lib(), TORCH_TO_GGML_HIDDEN[x.dtype], _stream(x.device)
+        native.check_seq(lib.ktb200_experts_gate_up(x.data_ptr(), ids.data_ptr(), top, self.gate.data_ptr(), self.up.data_ptr(), act.data_ptr(), T, self.width,
+                                                    self.ff, dt, st))
+        native.check_seq(lib.ktb200_experts_down(act.data_ptr(), ids.data_ptr(), weights.data_ptr(), top, self.down.data_ptr(), out.data_ptr(), T, self.width,
+                                                 self.ff, dt, st))
+        return out
+
+
+class KSoftmaxTopKMoE(nn.Module):
+    """router (operators/gate.KSoftmaxTopKGate) -> dense experts: a mixture-of-experts feed-forward without shared experts."""
+
+    def __init__(self, width: int, ff: int, experts: int, top: int, dtype=torch.bfloat16, device="cuda"):
+        super().__init__()
+        from .gate import KSoftmaxTopKGate
+        self.router = KSoftmaxTopKGate(width, experts, top, device=device)
+        self.experts = KExpertsDense(width, ff, experts, dtype=dtype, device=device)
+
+    def load(self, loader, prefix: str):
+        self.router.load(loader, prefix + "router")
+        self.experts.load(loader, prefix)
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        ids, w = self.router(h)
+        return self.experts(h, ids, w)

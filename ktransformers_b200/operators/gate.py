@@ -90,3 +90,28 @@ class KMoEGateB200(KMoEGate):
             C.byref(cfg), n, x.data_ptr(), idx.data_ptr(), wt.data_ptr(), None,
             bsz_tensor.data_ptr() if bsz_tensor is not None else None, torch.cuda.current_stream(x.device).cuda_stream))
         return idx, wt
+
+
+class KSoftmaxTopKGate(nn.Module):
+    """Soft-max over all experts, the `top` largest kept with their scores as weights (no re-scaling): the router kernel's
+    `scoring = softmax, topk_method = greedy, norm_topk_prob = 0, routed_scaling_factor = 1` case (DeepSeek-V2's gate,
+    archive/ktransformers/models/modeling_deepseek.py:386-459), as a plain module for models that are built on the operators
+    directly.  Logits are an fp32 GEMV over fp32 router weights."""
+
+    def __init__(self, width: int, experts: int, top: int, device="cuda"):
+        super().__init__()
+        self.width, self.experts, self.top = width, experts, top
+        self.weight = nn.Parameter(torch.empty((experts, width), dtype=torch.float32, device=device), requires_grad=False)
+
+    def load(self, loader, key: str):
+        self.weight.data.copy_(loader.load_tensor(key, "cpu").float())
+
+    def forward(self, x: torch.Tensor):
+        n = x.shape[0]
+        idx = torch.empty((n, self.top), dtype=torch.int64, device=x.device)
+        wt = torch.empty((n, self.top), dtype=torch.float32, device=x.device)
+        cfg = native.GateConfig(self.experts, self.width, self.top, 1, 1, _SCORING["softmax"], _TOPK["greedy"], 0, 1.0, self.weight.data_ptr(), None,
+                                TORCH_TO_GGML_HIDDEN[x.dtype])
+        native.check_seq(native.seq_lib().ktb200_moe_gate_forward(C.byref(cfg), n, x.data_ptr(), idx.data_ptr(), wt.data_ptr(), None, None,
+                                                                  torch.cuda.current_stream(x.device).cuda_stream))
+        return idx, wt

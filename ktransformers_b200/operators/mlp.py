@@ -1,0 +1,35 @@
+"""KPolyNormMLP — a two-matrix feed-forward whose activation is a cubic polynomial of per-token normalised powers:
+
+    z = W_up h ;  act = c0 N(z) + c1 N(z^2) + c2 N(z^3) + c3 ,  N(y) = y / sqrt(mean(y^2) + eps) over the ff values ;  W_down act
+
+The two products are library GEMMs; the activation is one `ktb200_poly_norm` launch (csrc/seq_ops.cu: the three mean squares
+and the polynomial in fp32, one rounding to the compute dtype).  (The reference's gated MLP: modeling_deepseek_v3.py:385-397.)"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from .. import native
+from .norm import GGML_OF
+
+
+class KPolyNormMLP(nn.Module):
+    def __init__(self, width: int, ff: int, eps: float, dtype=torch.bfloat16, device="cuda"):
+        super().__init__()
+        self.width, self.ff, self.eps = width, ff, eps
+        self.up = nn.Parameter(torch.empty((ff, width), dtype=dtype, device=device), requires_grad=False)
+        self.down = nn.Parameter(torch.empty((width, ff), dtype=dtype, device=device), requires_grad=False)
+        self.coef = nn.Parameter(torch.zeros(4, dtype=torch.float32, device=device), requires_grad=False)
+
+    def load(self, loader, prefix: str):
+        self.up.data.copy_(loader.load_tensor(prefix + "up", "cpu"))
+        self.down.data.copy_(loader.load_tensor(prefix + "down", "cpu"))
+        self.coef.data.copy_(loader.load_tensor(prefix + "act", "cpu").float())
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        z = F.linear(h, self.up)
+        a = torch.empty_like(z)
+        native.check_seq(native.seq_lib().ktb200_poly_norm(z.data_ptr(), a.data_ptr(), self.coef.data_ptr(), float(self.eps), z.shape[0], self.ff,
+                                                           GGML_OF[z.dtype], torch.cuda.current_stream(z.device).cuda_stream))
+        return F.linear(a, self.down)
