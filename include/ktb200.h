@@ -360,7 +360,8 @@ int ktb200_mla_kv_write(void* kv_cache, int page_size, const void* ckv, const vo
  *   wr_row[t] when >= 0 (the caller double-buffers the state rows so that no launch reads a row it writes).
  * ktb200_latent_prep: proj row = [q latent | kv latent | rotated key part | ...]; writes RMS-normed q latent to cq_out and the
  *   RMS-normed kv latent + the rotated key part (interleaved pairs over the first rot_dims, angle pos * inv_freq[i]) into the
- *   paged cache row  page_table[slot][pos / page_size] * page_size + pos % page_size  ([R + rot_dim] per row).
+ *   paged cache row  page_table[slot][(pos / page_size) % max_pages] * page_size + pos % page_size  ([R + rot_dim] per row; a
+ *   sequence's page table row is a ring, so a windowed sequence may grow past max_pages * page_size tokens).
  * ktb200_latent_window_attn: absorbed latent attention, sliding window (<= 0: none), soft-max sink (NULL: none);
  *   q [T][H][dim + rot_dim], q_abs [H][T][R], out [H][T][R]; splits > 1 cuts each key range into parts (decode with long
  *   windows) and needs ktb200_latent_window_attn_workspace bytes.

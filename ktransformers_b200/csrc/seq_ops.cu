@@ -99,7 +99,7 @@ __global__ void __launch_bounds__(256) latent_prep_kernel(const T* __restrict__ 
     const float ik = 1.0f / sqrtf(sk / (float)kv_rank + eps);
     for (int i = tid; i < q_rank; i += blockDim.x) cq_out[(long)t * q_rank + i] = from_f<T>(to_f(p[i]) * iq * to_f(qn_w[i]));
     const int ps = pos[t];
-    const long row = (long)page_table[(long)slot[t] * max_pages + ps / page_size] * page_size + ps % page_size;
+    const long row = (long)page_table[(long)slot[t] * max_pages + (ps / page_size) % max_pages] * page_size + ps % page_size;
     T* c = cache + row * (kv_rank + rot_dim);
     for (int i = tid; i < kv_rank; i += blockDim.x) c[i] = from_f<T>(to_f(p[q_rank + i]) * ik * to_f(kvn_w[i]));
     const T* kr = p + q_rank + kv_rank;

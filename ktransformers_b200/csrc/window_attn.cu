@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(kWinWarps * 32) latent_window_attn_kernel(cons
             const int j = jt + r;
             T* dst = tile + (long)r * RSP;
             if (j < j1) {
-                const T* src = cache + ((long)pt[j / p.page_size] * p.page_size + j % p.page_size) * RS;
+                const T* src = cache + ((long)pt[(j / p.page_size) % p.max_pages] * p.page_size + j % p.page_size) * RS;
                 if (words) {
                     const uint32_t* s4 = reinterpret_cast<const uint32_t*>(src);
                     uint32_t* d4 = reinterpret_cast<uint32_t*>(dst);

@@ -88,7 +88,8 @@ class PagedStateCache:
     cache and a previous-token row.
 
     * One pool of `num_pages` pages of `page_size` tokens; layer l's buffer is `[num_pages, page_size, row_widths[l]]` and all
-      layers share the page ids, so a sequence has ONE page table row (`page_table[slot]`, device int32).
+      layers share the page ids, so a sequence has ONE page table row (`page_table[slot]`, device int32), used as a ring:
+      logical page p sits in column `p % max_pages_per_seq`.
     * A sequence occupies a slot from `open()` to `close()`; `extend(slot, n)` reserves pages for the next n tokens and returns
       the first position; pages that fall wholly behind `window` (the largest look-back of any layer) are given back while the
       sequence is still running, and pages and slots are reused without being cleared: readers never look outside
@@ -135,7 +136,7 @@ class PagedStateCache:
         s = self._slot_of.pop(seq_id)
         n_pages = (self._len[s] + self.page_size - 1) // self.page_size
         for lp in range(self._first_page[s], n_pages):
-            self._free_pages.append(int(self._table_host[s, lp]))
+            self._free_pages.append(int(self._table_host[s, lp % self.max_pages_per_seq]))
         self._len[s] = 0
         self._free_slots.append(s)
 
@@ -154,12 +155,12 @@ class PagedStateCache:
         start = self._len[slot]
         have = (start + self.page_size - 1) // self.page_size
         need = (start + n + self.page_size - 1) // self.page_size
-        if need > self.max_pages_per_seq:
-            raise MemoryError("PagedStateCache: sequence longer than the page table")
+        if need - self._first_page[slot] > self.max_pages_per_seq:      # the table row is a ring over the live pages
+            raise MemoryError("PagedStateCache: sequence holds more pages than its page table row")
         if need - have > len(self._free_pages):
             raise MemoryError("PagedStateCache: out of pages")
         for lp in range(have, need):
-            self._table_host[slot, lp] = self._free_pages.pop()
+            self._table_host[slot, lp % self.max_pages_per_seq] = self._free_pages.pop()
             self._dirty = True
         self._len[slot] = start + n
         self._touched.add(slot)
@@ -171,7 +172,7 @@ class PagedStateCache:
             return
         keep_from = max(0, self._len[slot] - (self.window - 1)) // self.page_size   # first page the NEXT token may read
         for lp in range(self._first_page[slot], keep_from):
-            self._free_pages.append(int(self._table_host[slot, lp]))
+            self._free_pages.append(int(self._table_host[slot, lp % self.max_pages_per_seq]))
         self._first_page[slot] = max(self._first_page[slot], keep_from)
 
     def sync_table(self) -> torch.Tensor:
