@@ -423,7 +423,15 @@ def main():
     ap.add_argument("--ctx", type=int, default=4096, help="cached tokens per sequence in the whole-step leg")
     ap.add_argument("--no-full-step", action="store_true")
     ap.add_argument("--no-prefill", action="store_true", help="skip the 1024-token grouped-GEMM leg")
+    ap.add_argument("--model", default=None, choices=["lekapel"],
+                    help="instead of the default workload: prefill / decode throughput and per-kernel rooflines of that model family "
+                         "(random weights) beside the DeepSeek path's kernels at equal size")
+    ap.add_argument("--sizes", default=None, help="with --model: comma-separated size names (default: all)")
     args = ap.parse_args()
+    if args.model is not None:
+        from ktransformers_b200.util import model_bench
+        model_bench.run(args)
+        return
     # This process owns the GPU and decodes on ONE stream: the persistent MoE-block kernel is launched as a plain grid
     # with programmatic dependent launch (its 148 CTAs become co-resident as the previous layer's CTAs exit) instead of
     # cooperatively — the cooperative attribute (library default: safe when several streams share the GPU) makes every

@@ -363,7 +363,7 @@ int ktb200_mla_kv_write(void* kv_cache, int page_size, const void* ckv, const vo
  *   paged cache row  page_table[slot][(pos / page_size) % max_pages] * page_size + pos % page_size  ([R + rot_dim] per row; a
  *   sequence's page table row is a ring, so a windowed sequence may grow past max_pages * page_size tokens).
  * ktb200_latent_window_attn: absorbed latent attention, sliding window (<= 0: none), soft-max sink (NULL: none);
- *   q [T][H][dim + rot_dim], q_abs [H][T][R], out [H][T][R]; splits > 1 cuts each key range into parts (decode with long
+ *   q [T][H][dim + rot_dim], q_abs [T][H][R], out [T][H][R]; splits > 1 cuts each key range into parts (decode with long
  *   windows) and needs ktb200_latent_window_attn_workspace bytes.
  * ktb200_sigmoid_gate_mul: out[t][h*vdim + d] = heads[h][t][d] * sigmoid(gate[t*gate_stride + h*vdim + d]).
  * ktb200_poly_norm: out = c0 N(z) + c1 N(z^2) + c2 N(z^3) + c3 per row, N(y) = y / sqrt(mean(y^2) + eps).
@@ -381,6 +381,15 @@ int ktb200_latent_window_attn(const void* q, const void* q_abs, int num_heads, i
                               const double* inv_freq, float scale, const float* sink, int window, const int* pos, const int* slot,
                               const int* page_table, int max_pages, int page_size, const void* cache, void* out, int n_tokens, int splits,
                               void* workspace, int dtype, void* stream);
+ /* ktb200_latent_window_attn_tc: the tcgen05 MLA decode kernel (mla.cu) for the same attention when kv_rank = 512, rot_dim = 64,
+ *   bf16 and page_size % 32 == 0: q_abs [T][H][512], q_rot [T][H][64] already rotated (ktb200_rope_rows), out [T][H][512];
+ *   probabilities enter the tensor core as hi + lo bf16 terms; workspace: ktb200_latent_window_attn_tc_workspace bytes. */
+size_t ktb200_latent_window_attn_tc_workspace(int n_tokens, int num_heads, int window, int max_kv);
+int ktb200_latent_window_attn_tc(const void* q_abs, const void* q_rot, int num_heads, float scale, const float* sink, int window, const int* pos,
+                                 const int* slot, const int* page_table, int max_pages, int page_size, const void* cache, long cache_rows,
+                                 void* out, int n_tokens, int max_kv, void* workspace, size_t workspace_bytes, void* stream);
+int ktb200_rope_rows(const void* q, int num_heads, int dim, int rot_dim, int rot_dims, const double* inv_freq, const int* pos, void* out,
+                     int n_tokens, int dtype, void* stream);
 int ktb200_sigmoid_gate_mul(const void* heads, const void* gate, long gate_stride, void* out, int n_tokens, int num_heads, int vdim,
                             int dtype, void* stream);
 int ktb200_poly_norm(const void* z, void* out, const float* coef, float eps, int n_tokens, int ff, int dtype, void* stream);

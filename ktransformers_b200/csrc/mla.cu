@@ -38,7 +38,7 @@ constexpr int kDK = 576;             // 512 latent + 64 rope
 constexpr int kDV = 512;
 constexpr int kHG = 64;              // heads per CTA (UMMA M of S)
 constexpr int kLT = 32;              // kv tokens per tile (UMMA N of S, K of O^T)
-constexpr int kStages = 4;
+constexpr int kMaxStages = 4;        // KV ring: 4 stages (3 when the probabilities are split, see SPLITP)
 constexpr int kChunks = kDK / 64;    // 9 column chunks of 64 bf16 = 128 B (one swizzle row)
 constexpr int kMlaThreads = 192;
 constexpr int kStageBytes = kLT * kDK * 2;         // 36,864 = 9 regions of 32 rows x 128 B
@@ -46,23 +46,21 @@ constexpr int kKRegion = kLT * 128;                // 4,096
 constexpr int kQRegion = kHG * 128;                // 8,192
 constexpr int kQBytes = kHG * kDK * 2;             // 73,728
 constexpr int kPBytes = kHG * kLT * 2;             // 4,096: [8 head groups][4 token groups][8 heads][8 tokens]
-constexpr int kOffQ = kStages * kStageBytes;       // 147,456
-constexpr int kOffP = kOffQ + kQBytes;             // 221,184
-constexpr int kOffMisc = kOffP + 2 * kPBytes;      // 229,376 (P is double-buffered)
+constexpr int kOffMiscMax = kMaxStages * kStageBytes + kQBytes + 2 * kPBytes;   // 229,376 (P is double-buffered)
 constexpr int kTmemCols = 512;
 constexpr int kColO = 0, kColS = 256;
 constexpr int kSChains = 4;          // independent partial-score accumulators per S buffer
 constexpr float kRescaleThreshold = 8.f;
 
 struct MlaMisc {
-    unsigned long long k_full[kStages], k_empty[kStages], s_full[2], s_empty[2], p_full, p_free[2];
+    unsigned long long k_full[kMaxStages], k_empty[kMaxStages], s_full[2], s_empty[2], p_full, p_free[2];
     uint32_t tmem_base;
     int need[2][4];
     float alpha[kHG];     // per head: 2^(m_ref_old - m_ref_new) of the current rescale
     float l[kHG];         // final row sums
     float m[kHG];         // final reference maxima
 };
-constexpr int kMlaSmem = kOffMisc + (int)sizeof(MlaMisc) + 1024;   // + slack to align the base to 1024 B
+constexpr int kMlaSmem = kOffMiscMax + (int)sizeof(MlaMisc) + 1024;   // + slack to align the base to 1024 B (both variants fit)
 static_assert(kMlaSmem <= 232448, "shared memory budget");
 
 struct MlaKParams {
@@ -75,6 +73,11 @@ struct MlaKParams {
     float* o_part;                 // [B][splits][Hq][512]
     float* lse_part;               // [B][splits][Hq]  (base-2)
     float* debug;                  // optional: S of the first tile [64][32], P bytes, see ktb200_debug_mla
+    // windowed / ragged use (ktb200_latent_window_attn_tc); all zero for plain MLA decode
+    const int* pos;                // kv_len == NULL: item b is a token at position pos[b] that sees [max(0, pos - window + 1), pos]
+    const int* seq_row;            // page-table row of item b (NULL: b)
+    int window;                    // <= 0: no lower bound
+    int ring;                      // the page-table row is a ring over logical pages (no clamp of the length to its capacity)
 };
 
 __device__ __forceinline__ float ex2(float x) {   // 2^x, one MUFU (x = -inf -> 0)
@@ -92,7 +95,16 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
+// SPLITP: the probabilities go to the tensor core as TWO bf16 terms, p = hi + lo (lo = bf16(p - hi)), so that P.V carries
+// ~16 mantissa bits of p instead of 8 (designs that keep attention weights in 32-bit); the second P buffer pair is paid
+// for with one stage of the KV ring.
+template <bool SPLITP>
 __global__ void __launch_bounds__(kMlaThreads, 1) mla_decode_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const MlaKParams p) {
+    constexpr int kStages = SPLITP ? 3 : 4;
+    constexpr int kOffQ = kStages * kStageBytes;
+    constexpr int kPStride = SPLITP ? 2 * kPBytes : kPBytes;      // hi | lo
+    constexpr int kOffP = kOffQ + kQBytes;
+    constexpr int kOffMisc = kOffP + 2 * kPStride;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;           // 128-byte swizzle atoms are 1024-byte aligned
@@ -103,11 +115,13 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_decode_tc_kernel(const __g
     const int h0 = hg * kHG;
     griddep_launch_dependents();
     griddep_wait();          // q, the newest cache row and kv_len come from the kernels before this one
-    int L = p.kv_len[b];
-    if (L > p.max_pages * p.page_size) L = p.max_pages * p.page_size;
-    const int ntiles = (L + kLT - 1) / kLT;
-    const int tiles_per = (ntiles + p.num_splits - 1) / p.num_splits;
-    const int tile0 = split * tiles_per, tile1 = min(ntiles, tile0 + tiles_per);
+    int L = p.kv_len ? p.kv_len[b] : p.pos[b] + 1;
+    if (!p.ring && L > p.max_pages * p.page_size) L = p.max_pages * p.page_size;
+    const int L0 = (p.window > 0 && L > p.window) ? L - p.window : 0;      // keys before L0 are outside the window
+    const long prow = (long)(p.seq_row ? p.seq_row[b] : b) * p.max_pages;  // this item's page-table row
+    const int ntiles = (L + kLT - 1) / kLT, tile_lo = L0 / kLT;
+    const int tiles_per = (ntiles - tile_lo + p.num_splits - 1) / p.num_splits;
+    const int tile0 = tile_lo + split * tiles_per, tile1 = min(ntiles, tile0 + tiles_per);
     const int n = tile1 - tile0;
     float* o_out = p.o_part + (((long)b * p.num_splits + split) * p.num_heads + h0) * kDV;
     float* lse_out = p.lse_part + ((long)b * p.num_splits + split) * p.num_heads + h0;
@@ -137,7 +151,7 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_decode_tc_kernel(const __g
         // the first tiles do not depend on anything set up below: request them now
         for (int j = 0; j < n && j < kStages; j++) {
             const int t_base = (tile0 + j) * kLT;
-            const int page = p.page_table[(long)b * p.max_pages + t_base / p.page_size];
+            const int page = p.page_table[prow + (t_base / p.page_size) % p.max_pages];
             const int row = page * p.page_size + t_base % p.page_size;
             const uint32_t bar = smem_u32(&misc.k_full[j]);
             bar_expect_tx(bar, kStageBytes);
@@ -192,7 +206,7 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_decode_tc_kernel(const __g
                 const int s = j % kStages;
                 bar_wait(smem_u32(&misc.k_empty[s]), ((j / kStages) & 1) ^ 1);
                 const int t_base = (tile0 + j) * kLT;
-                const int page = p.page_table[(long)b * p.max_pages + t_base / p.page_size];
+                const int page = p.page_table[prow + (t_base / p.page_size) % p.max_pages];
                 const int row = page * p.page_size + t_base % p.page_size;
                 const uint32_t bar = smem_u32(&misc.k_full[s]);
                 bar_expect_tx(bar, kStageBytes);
@@ -227,13 +241,17 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_decode_tc_kernel(const __g
                 bar_wait(smem_u32(&misc.p_full), j & 1);
                 tc_fence_after();
                 const int s = j % kStages;
-                const uint32_t kb = base + s * kStageBytes, pb = base + kOffP + (j & 1) * kPBytes;
+                const uint32_t kb = base + s * kStageBytes, pb = base + kOffP + (j & 1) * kPStride;
 #pragma unroll
                 for (int m = 0; m < 4; m++)
 #pragma unroll
-                    for (int k = 0; k < 2; k++)
+                    for (int k = 0; k < 2; k++) {
                         mma_f16(tmem + kColO + m * kHG, smem_desc(kb + 2 * m * kKRegion + k * 2048, kKRegion, 1024, kLayoutSw128),
                                 smem_desc(pb + k * 256, 128, 512, kLayoutNone), idesc_pv, (j | k) != 0);
+                        if (SPLITP)
+                            mma_f16(tmem + kColO + m * kHG, smem_desc(kb + 2 * m * kKRegion + k * 2048, kKRegion, 1024, kLayoutSw128),
+                                    smem_desc(pb + kPBytes + k * 256, 128, 512, kLayoutNone), idesc_pv, 1);
+                    }
                 mma_commit(smem_u32(&misc.k_empty[s]));
                 mma_commit(smem_u32(&misc.p_free[j & 1]));
                 if (p.debug && lane == 0 && split == 0 && hg == 0 && b == 0 && j < 60) reinterpret_cast<unsigned long long*>(p.debug + 2048)[128 + j] = gtime();
@@ -282,7 +300,7 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_decode_tc_kernel(const __g
             for (int i = 0; i < 16; i++) {
                 const uint32_t hi = __shfl_sync(0xffffffffu, sv[16 + i], lane & 15);
                 const float v = __uint_as_float(upper ? hi : sv[i]);
-                x[i] = (t_base + i < L) ? v * p.scale_log2 : -INFINITY;
+                x[i] = (t_base + i < L && t_base + i >= L0) ? v * p.scale_log2 : -INFINITY;
                 mt = fmaxf(mt, x[i]);
             }
             mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 16));
@@ -321,18 +339,24 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_decode_tc_kernel(const __g
             if (j >= 2) bar_wait(smem_u32(&misc.p_free[buf]), ((j >> 1) & 1) ^ 1);
             {
                 float ps = 0.f;
-                uint32_t pk[8];
+                uint32_t pk[8], pl[8];
 #pragma unroll
                 for (int i = 0; i < 16; i += 2) {
                     const float p0 = ex2(x[i] - m_ref), p1 = ex2(x[i + 1] - m_ref);
                     ps += p0 + p1;
                     pk[i >> 1] = pack_bf16(p0, p1);
+                    if (SPLITP)   // what bf16 rounding dropped (exact in fp32), as a second bf16 term
+                        pl[i >> 1] = pack_bf16(p0 - __uint_as_float(pk[i >> 1] << 16), p1 - __uint_as_float(pk[i >> 1] & 0xffff0000u));
                 }
                 l += ps;
                 // P[head][token] as the K-major no-swizzle B operand: core matrix (8 heads x 8 tokens) = 128 contiguous bytes
-                uint8_t* prow = smem + kOffP + buf * kPBytes + (head >> 3) * 512 + (head & 7) * 16 + upper * 256;
-                *reinterpret_cast<uint4*>(prow) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                *reinterpret_cast<uint4*>(prow + 128) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                uint8_t* pdst = smem + kOffP + buf * kPStride + (head >> 3) * 512 + (head & 7) * 16 + upper * 256;
+                *reinterpret_cast<uint4*>(pdst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                *reinterpret_cast<uint4*>(pdst + 128) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                if (SPLITP) {
+                    *reinterpret_cast<uint4*>(pdst + kPBytes) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
+                    *reinterpret_cast<uint4*>(pdst + kPBytes + 128) = make_uint4(pl[4], pl[5], pl[6], pl[7]);
+                }
             }
             // rows of the tile beyond kv_len hold whatever the page contains: P is 0 there, but 0 * NaN is NaN -> zero the V rows
             if ((tile0 + j) * kLT + kLT > L) {
@@ -398,8 +422,9 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_decode_tc_kernel(const __g
 }
 
 // out[b][h][:] = sum_s w_s * o_part[b][s][h][:],  w_s = 2^(lse_s - max) / sum ; lse (natural log) optional
+// sink (optional, [num_heads], natural-log units): one more term exp(sink_h) in the denominator that carries no value
 __global__ void __launch_bounds__(128) mla_merge_kernel(const float* o_part, const float* lse_part, int num_splits, int num_heads,
-                                                        __nv_bfloat16* out, float* lse_out) {
+                                                        __nv_bfloat16* out, float* lse_out, const float* sink) {
     __shared__ float ws[128];
     __shared__ float red[8];
     griddep_launch_dependents();
@@ -413,6 +438,8 @@ __global__ void __launch_bounds__(128) mla_merge_kernel(const float* o_part, con
     if (lane == 0) red[warp] = mx;
     __syncthreads();
     mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    const float snk = sink ? sink[h] * 1.4426950408889634f : -INFINITY;
+    mx = fmaxf(mx, snk);
     const int c = tid * 4;
     __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(out + ((long)b * num_heads + h) * kDV + c);
     if (mx == -INFINITY) {   // kv_len == 0 (e.g. a padded CUDA-graph batch slot): zeros, lse = -inf
@@ -426,6 +453,7 @@ __global__ void __launch_bounds__(128) mla_merge_kernel(const float* o_part, con
     if (lane == 0) red[4 + warp] = den;
     __syncthreads();
     den = (red[4] + red[5]) + (red[6] + red[7]);
+    if (sink) den += exp2f(snk - mx);
     ws[tid] = e / den;
     __syncthreads();
     float4 acc = make_float4(0, 0, 0, 0);
@@ -492,6 +520,54 @@ size_t ktb200_mla_workspace_bytes(int batch, int num_heads, int max_splits) {
     return (size_t)batch * max_splits * num_heads * (ktb::kDV + 1) * sizeof(float);
 }
 
+// shared launch path of plain MLA decode and the windowed / ragged form
+static int mla_launch(const ktb::MlaKParams& in, const void* kv_cache, long kv_cache_rows, int batch, int num_kv_splits, int max_tiles, void* workspace,
+                      size_t workspace_bytes, void* out, float* lse_out, const float* sink, bool split_p, void* stream) {
+    using namespace ktb;
+    int dev = 0;
+    KTB_CUDA_CHECK(cudaGetDevice(&dev));
+    int splits = num_kv_splits > 0 ? num_kv_splits : pick_splits(batch, in.num_heads, max_tiles, dev);
+    if (splits > max_tiles) splits = max_tiles;
+    if (splits < 1) splits = 1;
+    const size_t need = (size_t)batch * splits * in.num_heads * (kDV + 1) * sizeof(float);
+    if (need > workspace_bytes) { set_error("mla_decode: workspace too small (%zu < %zu bytes for %d splits)", workspace_bytes, need, splits); return KTB200_EINVAL; }
+    cudaStream_t s = (cudaStream_t)stream;
+
+    // the paged cache as a 2-D tensor [token rows][576 columns]; a tile never crosses a page (page_size % 32 == 0)
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) { set_error("mla_decode: cuTensorMapEncodeTiled is not available from this driver"); return KTB200_ECUDA; }
+    CUtensorMap map;
+    const cuuint64_t rows = kv_cache_rows > 0 ? (cuuint64_t)kv_cache_rows : (cuuint64_t)1 << 31;
+    const cuuint64_t gdim[2] = {(cuuint64_t)kDK, rows};
+    const cuuint64_t gstr[1] = {(cuuint64_t)kDK * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)kLT};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult cr = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(kv_cache), gdim, gstr, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) { set_error("mla_decode: cuTensorMapEncodeTiled failed (%d)", (int)cr); return KTB200_ECUDA; }
+
+    MlaKParams p = in;
+    p.num_splits = splits;
+    p.o_part = (float*)workspace;
+    p.lse_part = p.o_part + (size_t)batch * splits * p.num_heads * kDV;
+    p.debug = g_mla_debug;
+    static bool attr_set[64] = {};
+    if (!attr_set[dev & 63]) {
+        KTB_CUDA_CHECK(cudaFuncSetAttribute(mla_decode_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmem));
+        KTB_CUDA_CHECK(cudaFuncSetAttribute(mla_decode_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmem));
+        attr_set[dev & 63] = true;
+    }
+    const int head_groups = (p.num_heads + kHG - 1) / kHG;
+    if (split_p) KTB_CUDA_CHECK(launch_pdl(mla_decode_tc_kernel<true>, dim3(splits, head_groups, batch), dim3(kMlaThreads), (size_t)kMlaSmem, s, map, p));
+    else KTB_CUDA_CHECK(launch_pdl(mla_decode_tc_kernel<false>, dim3(splits, head_groups, batch), dim3(kMlaThreads), (size_t)kMlaSmem, s, map, p));
+    count_launch();
+    KTB_CUDA_CHECK(launch_pdl(mla_merge_kernel, dim3(batch * p.num_heads), dim3(128), 0, s, (const float*)p.o_part, (const float*)p.lse_part, splits, p.num_heads,
+                              (__nv_bfloat16*)out, lse_out, sink));
+    count_launch();
+    return KTB200_OK;
+}
+
 int ktb200_mla_decode(const ktb200_mla_params* q, void* stream) {
     using namespace ktb;
     if (!q || !q->q_nope || !q->q_pe || !q->kv_cache || !q->page_table || !q->kv_len || !q->out || !q->workspace) { set_error("mla_decode: null pointer"); return KTB200_EINVAL; }
@@ -501,48 +577,44 @@ int ktb200_mla_decode(const ktb200_mla_params* q, void* stream) {
         return KTB200_EINVAL;
     }
     if (((uintptr_t)q->kv_cache & 15) || ((uintptr_t)q->q_nope & 15) || ((uintptr_t)q->q_pe & 15)) { set_error("mla_decode: q / kv_cache must be 16-byte aligned"); return KTB200_EINVAL; }
-    int dev = 0;
-    KTB_CUDA_CHECK(cudaGetDevice(&dev));
-    const int max_tiles = q->max_pages_per_seq * (q->page_size / kLT);
-    int splits = q->num_kv_splits > 0 ? q->num_kv_splits : pick_splits(q->batch, q->num_heads, max_tiles, dev);
-    if (splits > max_tiles) splits = max_tiles;
-    const size_t need = (size_t)q->batch * splits * q->num_heads * (kDV + 1) * sizeof(float);
-    if (need > q->workspace_bytes) { set_error("mla_decode: workspace too small (%zu < %zu bytes for %d splits)", q->workspace_bytes, need, splits); return KTB200_EINVAL; }
-    cudaStream_t s = (cudaStream_t)stream;
-
-    // the paged cache as a 2-D tensor [token rows][576 columns]; a tile never crosses a page (page_size % 32 == 0)
-    EncodeTiledFn enc = encode_tiled();
-    if (!enc) { set_error("mla_decode: cuTensorMapEncodeTiled is not available from this driver"); return KTB200_ECUDA; }
-    CUtensorMap map;
-    const cuuint64_t rows = q->kv_cache_rows > 0 ? (cuuint64_t)q->kv_cache_rows : (cuuint64_t)1 << 31;
-    const cuuint64_t gdim[2] = {(cuuint64_t)kDK, rows};
-    const cuuint64_t gstr[1] = {(cuuint64_t)kDK * 2};
-    const cuuint32_t box[2] = {64, (cuuint32_t)kLT};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUresult cr = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(q->kv_cache), gdim, gstr, box, estr,
-                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (cr != CUDA_SUCCESS) { set_error("mla_decode: cuTensorMapEncodeTiled failed (%d)", (int)cr); return KTB200_ECUDA; }
-
     MlaKParams p{};
     p.q_nope = (const __nv_bfloat16*)q->q_nope; p.q_pe = (const __nv_bfloat16*)q->q_pe;
     p.page_table = q->page_table; p.kv_len = q->kv_len; p.num_heads = q->num_heads; p.page_size = q->page_size;
-    p.max_pages = q->max_pages_per_seq; p.num_splits = splits; p.scale_log2 = q->sm_scale * 1.4426950408889634f;
-    p.o_part = (float*)q->workspace;
-    p.lse_part = p.o_part + (size_t)q->batch * splits * q->num_heads * kDV;
-    p.debug = g_mla_debug;
-    static bool attr_set[64] = {};
-    if (!attr_set[dev & 63]) {
-        KTB_CUDA_CHECK(cudaFuncSetAttribute(mla_decode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmem));
-        attr_set[dev & 63] = true;
-    }
-    const int head_groups = (q->num_heads + kHG - 1) / kHG;
-    KTB_CUDA_CHECK(launch_pdl(mla_decode_tc_kernel, dim3(splits, head_groups, q->batch), dim3(kMlaThreads), (size_t)kMlaSmem, s, map, p));
-    count_launch();
-    KTB_CUDA_CHECK(launch_pdl(mla_merge_kernel, dim3(q->batch * q->num_heads), dim3(128), 0, s, (const float*)p.o_part, (const float*)p.lse_part, splits, q->num_heads,
-                              (__nv_bfloat16*)q->out, q->lse_out));
-    count_launch();
-    return KTB200_OK;
+    p.max_pages = q->max_pages_per_seq; p.scale_log2 = q->sm_scale * 1.4426950408889634f;
+    return mla_launch(p, q->kv_cache, q->kv_cache_rows, q->batch, q->num_kv_splits, q->max_pages_per_seq * (q->page_size / kLT), q->workspace, q->workspace_bytes, q->out,
+                      q->lse_out, nullptr, false, stream);
+}
+
+// The same tensor-core kernel for a ragged batch of tokens with a sliding window and a soft-max sink: item t is a token of the
+// sequence in page-table row slot[t] at position pos[t]; it sees positions [max(0, pos - window + 1), pos] (window <= 0: from
+// 0); probabilities reach the tensor core as hi + lo bf16 terms; the sink joins in the merge.  q_abs [T][H][512], q_rot
+// [T][H][64] (already rotated), out [T][H][512], all bf16; page_size a multiple of 32; max_kv bounds pos + 1 (sizes the split).
+size_t ktb200_latent_window_attn_tc_workspace(int n_tokens, int num_heads, int window, int max_kv) {
+    using namespace ktb;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || n_tokens <= 0 || num_heads <= 0) return 0;
+    const int span = window > 0 && window < max_kv ? window : max_kv;
+    const int max_tiles = (span + kLT - 1) / kLT + 1;
+    int splits = pick_splits(n_tokens, num_heads, max_tiles, dev);
+    if (splits > max_tiles) splits = max_tiles;
+    if (splits < 1) splits = 1;
+    return (size_t)n_tokens * splits * num_heads * (kDV + 1) * sizeof(float);
+}
+
+int ktb200_latent_window_attn_tc(const void* q_abs, const void* q_rot, int num_heads, float scale, const float* sink, int window, const int* pos, const int* slot,
+                                 const int* page_table, int max_pages, int page_size, const void* cache, long cache_rows, void* out, int n_tokens, int max_kv,
+                                 void* workspace, size_t workspace_bytes, void* stream) {
+    using namespace ktb;
+    if (!q_abs || !q_rot || !pos || !slot || !page_table || !cache || !out || !workspace) { set_error("latent_window_attn_tc: null pointer"); return KTB200_EINVAL; }
+    if (n_tokens <= 0) return KTB200_OK;
+    if (num_heads <= 0 || page_size <= 0 || page_size % kLT || max_pages <= 0 || max_kv <= 0) { set_error("latent_window_attn_tc: bad argument (page_size a multiple of %d)", kLT); return KTB200_EINVAL; }
+    if (((uintptr_t)cache & 15) || ((uintptr_t)q_abs & 15) || ((uintptr_t)q_rot & 15)) { set_error("latent_window_attn_tc: q / cache must be 16-byte aligned"); return KTB200_EINVAL; }
+    MlaKParams p{};
+    p.q_nope = (const __nv_bfloat16*)q_abs; p.q_pe = (const __nv_bfloat16*)q_rot;
+    p.page_table = page_table; p.kv_len = nullptr; p.pos = pos; p.seq_row = slot; p.window = window; p.ring = 1;
+    p.num_heads = num_heads; p.page_size = page_size; p.max_pages = max_pages; p.scale_log2 = scale * 1.4426950408889634f;
+    const int span = window > 0 && window < max_kv ? window : max_kv;
+    return mla_launch(p, cache, cache_rows, n_tokens, 0, (span + kLT - 1) / kLT + 1, workspace, workspace_bytes, out, nullptr, sink, true, stream);
 }
 
 // Diagnostics: while set, CTA (split 0, head group 0, sequence 0) of ktb200_mla_decode writes the raw fp32 scores of its

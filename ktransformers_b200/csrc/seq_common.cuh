@@ -29,4 +29,46 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
+// Partial dot product of a weight row with a vector held in shared memory (fp32), over the columns this lane owns.  Rows whose
+// byte length is a multiple of 16 (and 16-byte aligned) stream as 16-byte read-only loads; any other row element by element.
+__device__ __forceinline__ float lane_dot(const __nv_bfloat16* __restrict__ w, const float* __restrict__ xs, int n, int lane, bool vec) {
+    float s = 0.f;
+    if (vec) {
+        for (int i = lane * 8; i < n; i += 256) {
+            const uint4 v = ldg_stream16(w + i);
+            const float4 a = *reinterpret_cast<const float4*>(xs + i), b = *reinterpret_cast<const float4*>(xs + i + 4);
+            s = fmaf(__uint_as_float(v.x << 16), a.x, s);
+            s = fmaf(__uint_as_float(v.x & 0xffff0000u), a.y, s);
+            s = fmaf(__uint_as_float(v.y << 16), a.z, s);
+            s = fmaf(__uint_as_float(v.y & 0xffff0000u), a.w, s);
+            s = fmaf(__uint_as_float(v.z << 16), b.x, s);
+            s = fmaf(__uint_as_float(v.z & 0xffff0000u), b.y, s);
+            s = fmaf(__uint_as_float(v.w << 16), b.z, s);
+            s = fmaf(__uint_as_float(v.w & 0xffff0000u), b.w, s);
+        }
+    } else {
+        for (int i = lane; i < n; i += 32) s = fmaf(__bfloat162float(w[i]), xs[i], s);
+    }
+    return s;
+}
+__device__ __forceinline__ float lane_dot(const float* __restrict__ w, const float* __restrict__ xs, int n, int lane, bool vec) {
+    float s = 0.f;
+    if (vec) {
+        for (int i = lane * 4; i < n; i += 128) {
+            const uint4 v = ldg_stream16(w + i);
+            const float4 a = *reinterpret_cast<const float4*>(xs + i);
+            s = fmaf(__uint_as_float(v.x), a.x, s);
+            s = fmaf(__uint_as_float(v.y), a.y, s);
+            s = fmaf(__uint_as_float(v.z), a.z, s);
+            s = fmaf(__uint_as_float(v.w), a.w, s);
+        }
+    } else {
+        for (int i = lane; i < n; i += 32) s = fmaf(w[i], xs[i], s);
+    }
+    return s;
+}
+template <typename T> __device__ __forceinline__ bool rows_vectorise(const T* base, int n) {
+    return (n * sizeof(T)) % 16 == 0 && (reinterpret_cast<uintptr_t>(base) & 15) == 0;
+}
+
 }  // namespace ktb

@@ -21,15 +21,19 @@
 namespace ktb {
 
 // ------------------------------------------------------------------------------------------------ norm + token shift
-// One CTA per token.  smem: inv[2][groups] | red
+// One CTA per token.  smem: inv[2][groups] | (stash) row[D] | prev row[D].  With `stash` the row (after the residual sum) and the
+// previous token's row are read from global memory ONCE by all threads and kept in shared memory for the group sums and the
+// output pass; rows too wide for shared memory are re-read instead.
 template <typename T>
 __global__ void __launch_bounds__(256) group_norm_shift_kernel(const float* __restrict__ x_in, const void* da, int a_type, const void* db, int b_type, float mult,
                                                                float* __restrict__ x_out, const T* __restrict__ w, int groups, float eps, const T* __restrict__ mu,
                                                                const int* __restrict__ prev_idx, const int* __restrict__ rd_row, const int* __restrict__ wr_row,
-                                                               float* __restrict__ state, T* __restrict__ h_out, T* __restrict__ hs_out, int D) {
-    extern __shared__ float sm[];
+                                                               float* __restrict__ state, T* __restrict__ h_out, T* __restrict__ hs_out, int D, int stash) {
+    extern __shared__ __align__(16) float sm[];
     float* inv_cur = sm;
     float* inv_prev = sm + groups;
+    float* cur = sm + 2 * groups;
+    float* prv = cur + D;
     const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
     const int gs = D / groups;
     const bool add = da != nullptr || db != nullptr;
@@ -44,13 +48,20 @@ __global__ void __launch_bounds__(256) group_norm_shift_kernel(const float* __re
         }
         return v;
     };
+    if (stash) {
+        for (int i = tid; i < D; i += blockDim.x) {
+            cur[i] = row_val(t, i);
+            if (pi >= 0) prv[i] = row_val(pi, i);
+        }
+        __syncthreads();
+    }
     for (int g = warp; g < groups; g += nw) {
         float sc = 0.f, sp = 0.f;
         for (int i = lane; i < gs; i += 32) {
-            const float v = row_val(t, g * gs + i);
+            const float v = stash ? cur[g * gs + i] : row_val(t, g * gs + i);
             sc += v * v;
             if (pi >= 0) {
-                const float u = row_val(pi, g * gs + i);
+                const float u = stash ? prv[g * gs + i] : row_val(pi, g * gs + i);
                 sp += u * u;
             }
         }
@@ -65,14 +76,14 @@ __global__ void __launch_bounds__(256) group_norm_shift_kernel(const float* __re
     const int rr = (mu && rd_row) ? rd_row[t] : -1;
     const int wr = (mu && wr_row) ? wr_row[t] : -1;
     for (int i = tid; i < D; i += blockDim.x) {
-        const float v = row_val(t, i);
+        const float v = stash ? cur[i] : row_val(t, i);
         if (add && x_out) x_out[(long)t * D + i] = v;
         const float wi = to_f(w[i]);
         const float h = v * inv_cur[i / gs] * wi;
         if (h_out) h_out[(long)t * D + i] = from_f<T>(h);
         if (mu) {
             float hp = 0.f;
-            if (pi >= 0) hp = row_val(pi, i) * inv_prev[i / gs] * wi;
+            if (pi >= 0) hp = (stash ? prv[i] : row_val(pi, i)) * inv_prev[i / gs] * wi;
             else if (rr >= 0) hp = state[(long)rr * D + i];
             if (hs_out) hs_out[(long)t * D + i] = from_f<T>(h + (hp - h) * to_f(mu[i]));
             if (wr >= 0) state[(long)wr * D + i] = h;
@@ -115,6 +126,27 @@ __global__ void __launch_bounds__(256) latent_prep_kernel(const T* __restrict__ 
     }
 }
 
+// ------------------------------------------------------------------------------------------------ rotated query part
+// out[t][h][:] = rot(q[t][h][dn : dn + dr]) at position pos[t] (interleaved pairs over the first rot_dims columns)
+template <typename T>
+__global__ void rope_rows_kernel(const T* __restrict__ q, int H, int dn, int dr, int rot_dims, const double* __restrict__ inv_freq, const int* __restrict__ pos,
+                                 T* __restrict__ out, int n_tokens) {
+    const long n = (long)n_tokens * H * dr;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+        const int d = (int)(i % dr);
+        const long th = i / dr;
+        const T* src = q + th * (dn + dr) + dn;
+        float v = to_f(src[d]);
+        if (d < rot_dims) {
+            double sn, cs;
+            sincos((double)pos[th / H] * inv_freq[d >> 1], &sn, &cs);
+            const float other = to_f(src[d ^ 1]);
+            v = (d & 1) ? v * (float)cs + other * (float)sn : v * (float)cs - other * (float)sn;
+        }
+        out[i] = from_f<T>(v);
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ output gate
 template <typename T>
 __global__ void sigmoid_gate_mul_kernel(const T* __restrict__ heads, const T* __restrict__ gate, long gate_stride, T* __restrict__ out, int n_tokens, int H, int dv) {
@@ -153,7 +185,7 @@ __global__ void __launch_bounds__(256) poly_norm_kernel(const T* __restrict__ z,
 template <typename T>
 __global__ void __launch_bounds__(256) experts_gate_up_kernel(const T* __restrict__ x, const int64_t* __restrict__ ids, int top, const T* __restrict__ Wg, const T* __restrict__ Wu,
                                                               T* __restrict__ act, int D, int F) {
-    extern __shared__ float xs[];
+    extern __shared__ __align__(16) float xs[];
     const long p = blockIdx.x;
     const long t = p / top;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -162,12 +194,10 @@ __global__ void __launch_bounds__(256) experts_gate_up_kernel(const T* __restric
     const long e = ids[p];
     const T* g = Wg + e * (long)F * D;
     const T* u = Wu + e * (long)F * D;
+    const bool vec = rows_vectorise(Wg, D) && rows_vectorise(Wu, D);
     for (int r = blockIdx.y * nw + warp; r < F; r += gridDim.y * nw) {
-        float sg = 0.f, su = 0.f;
-        for (int i = lane; i < D; i += 32) {
-            sg += to_f(g[(long)r * D + i]) * xs[i];
-            su += to_f(u[(long)r * D + i]) * xs[i];
-        }
+        float sg = lane_dot(g + (long)r * D, xs, D, lane, vec);
+        float su = lane_dot(u + (long)r * D, xs, D, lane, vec);
         sg = warp_sum(sg);
         su = warp_sum(su);
         if (lane == 0) act[p * F + r] = from_f<T>(act_silu(sg) * su);
@@ -178,18 +208,17 @@ __global__ void __launch_bounds__(256) experts_gate_up_kernel(const T* __restric
 template <typename T>
 __global__ void __launch_bounds__(256) experts_down_kernel(const T* __restrict__ act, const int64_t* __restrict__ ids, const float* __restrict__ wts, int top,
                                                            const T* __restrict__ Wd, float* __restrict__ out, int D, int F) {
-    extern __shared__ float as[];   // [top][F]
+    extern __shared__ __align__(16) float as[];   // [top][F]
     const long t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     for (int i = threadIdx.x; i < top * F; i += blockDim.x) as[i] = to_f(act[t * top * F + i]);
     __syncthreads();
+    const bool vec = rows_vectorise(Wd, F);
     for (int d = blockIdx.y * nw + warp; d < D; d += gridDim.y * nw) {
         float acc = 0.f;
         for (int j = 0; j < top; j++) {
             const T* wd = Wd + (ids[t * top + j] * (long)D + d) * F;
-            float s = 0.f;
-            for (int i = lane; i < F; i += 32) s += to_f(wd[i]) * as[j * F + i];
-            s = warp_sum(s);
+            float s = warp_sum(lane_dot(wd, as + j * F, F, lane, vec));
             acc = fmaf(wts[t * top + j], s, acc);
         }
         if (lane == 0) out[t * D + d] = acc;
@@ -214,9 +243,14 @@ extern "C" int ktb200_group_rmsnorm_shift(const float* x_in, const void* delta_a
     if ((delta_a || delta_b) && (!x_out || x_out == x_in)) { set_error("group_rmsnorm_shift: the sum needs a separate output row buffer"); return KTB200_EINVAL; }
     if (shift && (!prev_idx || !rd_row || !wr_row || !state || !hs_out)) { set_error("group_rmsnorm_shift: shift needs its index rows, state and output"); return KTB200_EINVAL; }
     if (n_tokens == 0) return KTB200_OK;
-    const size_t smem = 2 * (size_t)groups * sizeof(float);
-    SEQ_DISPATCH(dtype, (group_norm_shift_kernel<T><<<n_tokens, 256, smem, (cudaStream_t)stream>>>(x_in, delta_a, a_type, delta_b, b_type, mult, x_out, (const T*)weight, groups, eps,
-                                                                                                   (const T*)shift, prev_idx, rd_row, wr_row, state, (T*)h_out, (T*)hs_out, width)));
+    size_t smem = 2 * (size_t)groups * sizeof(float);
+    const int stash = smem + 2 * (size_t)width * sizeof(float) <= 160 * 1024;
+    if (stash) smem += 2 * (size_t)width * sizeof(float);
+    SEQ_DISPATCH(dtype, {
+        if (smem > 48 * 1024) KTB_CUDA_CHECK(cudaFuncSetAttribute(group_norm_shift_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        group_norm_shift_kernel<T><<<n_tokens, 256, smem, (cudaStream_t)stream>>>(x_in, delta_a, a_type, delta_b, b_type, mult, x_out, (const T*)weight, groups, eps,
+                                                                                  (const T*)shift, prev_idx, rd_row, wr_row, state, (T*)h_out, (T*)hs_out, width, stash);
+    });
     KTB_LAUNCH_CHECK();
     return KTB200_OK;
 }
@@ -232,6 +266,20 @@ extern "C" int ktb200_latent_prep(const void* proj, long proj_stride, int q_rank
     if (n_tokens <= 0) return KTB200_OK;
     SEQ_DISPATCH(dtype, (latent_prep_kernel<T><<<n_tokens, 256, 0, (cudaStream_t)stream>>>((const T*)proj, proj_stride, q_rank, kv_rank, rot_dim, rot_dims, inv_freq, (const T*)q_norm_w,
                                                                                            (const T*)kv_norm_w, eps, pos, slot, page_table, max_pages, page_size, (T*)cache, (T*)cq_out)));
+    KTB_LAUNCH_CHECK();
+    return KTB200_OK;
+}
+
+extern "C" int ktb200_rope_rows(const void* q, int num_heads, int dim, int rot_dim, int rot_dims, const double* inv_freq, const int* pos, void* out, int n_tokens, int dtype,
+                                void* stream) {
+    if (!q || !pos || !out || num_heads <= 0 || dim < 0 || rot_dim <= 0 || rot_dims < 0 || rot_dims > rot_dim || (rot_dims & 1) || (rot_dims && !inv_freq)) {
+        set_error("rope_rows: bad argument");
+        return KTB200_EINVAL;
+    }
+    if (n_tokens <= 0) return KTB200_OK;
+    const long n = (long)n_tokens * num_heads * rot_dim;
+    const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+    SEQ_DISPATCH(dtype, (rope_rows_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>((const T*)q, num_heads, dim, rot_dim, rot_dims, inv_freq, pos, (T*)out, n_tokens)));
     KTB_LAUNCH_CHECK();
     return KTB200_OK;
 }
@@ -259,7 +307,8 @@ extern "C" int ktb200_experts_gate_up(const void* x, const int64_t* ids, int top
     if (!x || !ids || !w_gate || !w_up || !act || top <= 0 || width <= 0 || ff <= 0 || width * sizeof(float) > 200 * 1024) { set_error("experts_gate_up: bad argument"); return KTB200_EINVAL; }
     if (n_tokens <= 0) return KTB200_OK;
     const size_t smem = (size_t)width * sizeof(float);
-    const int ry = (ff + 7) / 8 < 16 ? (ff + 7) / 8 : 16;
+    int ry = (ff + 7) / 8;   // row blocks: enough CTAs to fill 148 SMs several times over when there are few pairs
+    { const int want = (148 * 8 + n_tokens * top - 1) / (n_tokens * top); if (ry > want) ry = want; if (ry < 1) ry = 1; }
     SEQ_DISPATCH(dtype, {
         if (smem > 48 * 1024) KTB_CUDA_CHECK(cudaFuncSetAttribute(experts_gate_up_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         experts_gate_up_kernel<T><<<dim3(n_tokens * top, ry), 256, smem, (cudaStream_t)stream>>>((const T*)x, ids, top, (const T*)w_gate, (const T*)w_up, (T*)act, width, ff);
@@ -273,7 +322,8 @@ extern "C" int ktb200_experts_down(const void* act, const int64_t* ids, const fl
     if (!act || !ids || !weights || !w_down || !out || top <= 0 || width <= 0 || ff <= 0 || (size_t)top * ff * sizeof(float) > 200 * 1024) { set_error("experts_down: bad argument"); return KTB200_EINVAL; }
     if (n_tokens <= 0) return KTB200_OK;
     const size_t smem = (size_t)top * ff * sizeof(float);
-    const int ry = (width + 7) / 8 < 16 ? (width + 7) / 8 : 16;
+    int ry = (width + 7) / 8;
+    { const int want = (148 * 8 + n_tokens - 1) / n_tokens; if (ry > want) ry = want; if (ry < 1) ry = 1; }
     SEQ_DISPATCH(dtype, {
         if (smem > 48 * 1024) KTB_CUDA_CHECK(cudaFuncSetAttribute(experts_down_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         experts_down_kernel<T><<<dim3(n_tokens, ry), 256, smem, (cudaStream_t)stream>>>((const T*)act, ids, weights, top, (const T*)w_down, out, width, ff);

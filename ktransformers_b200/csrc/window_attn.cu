@@ -24,14 +24,14 @@ namespace ktb {
 
 struct WinAttnParams {
     const void* q;        // [T][H][dn + dr]
-    const void* q_abs;    // [H][T][R]
+    const void* q_abs;    // [T][H][R]
     const double* inv_freq;
     const float* sink;    // [H] or null
     const int* pos;
     const int* slot;
     const int* page_table;
     const void* cache;    // [pages][page_size][R + dr]
-    void* out;            // [H][T][R]
+    void* out;            // [T][H][R]
     float* part;          // split path: [T][H][splits][R + 2]
     int T, H, dn, dr, R, rot_dims, window, max_pages, page_size, row_pad, splits;
     float scale;
@@ -72,11 +72,13 @@ __global__ void __launch_bounds__(kWinWarps * 32) latent_window_attn_kernel(cons
             }
             qr[warp * dr + i] = v;
         }
-        const T* a = reinterpret_cast<const T*>(p.q_abs) + ((long)h * p.T + t) * R;
+        const T* a = reinterpret_cast<const T*>(p.q_abs) + ((long)t * p.H + h) * R;
         for (int i = lane; i < R; i += 32) qa[warp * R + i] = to_f(a[i]);
     }
     float m = (!SPLIT && p.sink && live) ? p.sink[h] : -INFINITY;
     float l = (!SPLIT && p.sink && live) ? 1.0f : 0.0f;
+    constexpr int VW = sizeof(T) == 2 ? 2 : 1;      // bf16: a lane owns column PAIRS (32-bit shared-memory loads in the value phase)
+    auto col = [&](int i) { return VW == 2 ? 2 * (lane + 32 * (i >> 1)) + (i & 1) : lane + 32 * i; };
     float acc[NI];
 #pragma unroll
     for (int i = 0; i < NI; i++) acc[i] = 0.f;
@@ -107,9 +109,25 @@ __global__ void __launch_bounds__(kWinWarps * 32) latent_window_attn_kernel(cons
         {
             const T* kr = tile + (long)lane * RSP;
             const float* a = qa + warp * R;
-            for (int d = 0; d < R; d++) s = fmaf(a[d], to_f(kr[d]), s);
             const float* b = qr + warp * dr;
-            for (int d = 0; d < dr; d++) s = fmaf(b[d], to_f(kr[R + d]), s);
+            if (sizeof(T) == 2 && !(R & 1) && !(dr & 1)) {     // two bf16 per 32-bit shared-memory load
+                const uint32_t* k2 = reinterpret_cast<const uint32_t*>(kr);
+                for (int d = 0; d < R; d += 2) {
+                    const uint32_t w = k2[d >> 1];
+                    const float2 q2 = *reinterpret_cast<const float2*>(a + d);
+                    s = fmaf(q2.x, __uint_as_float(w << 16), s);
+                    s = fmaf(q2.y, __uint_as_float(w & 0xffff0000u), s);
+                }
+                k2 += R >> 1;
+                for (int d = 0; d < dr; d += 2) {
+                    const uint32_t w = k2[d >> 1];
+                    s = fmaf(b[d], __uint_as_float(w << 16), s);
+                    s = fmaf(b[d + 1], __uint_as_float(w & 0xffff0000u), s);
+                }
+            } else {
+                for (int d = 0; d < R; d++) s = fmaf(a[d], to_f(kr[d]), s);
+                for (int d = 0; d < dr; d++) s = fmaf(b[d], to_f(kr[R + d]), s);
+            }
         }
         s = (jt + lane < j1) ? s * p.scale : -INFINITY;
         const float mn = fmaxf(m, warp_max(s));
@@ -125,10 +143,23 @@ __global__ void __launch_bounds__(kWinWarps * 32) latent_window_attn_kernel(cons
         for (int j = 0; j < nk; j++) {
             const float w = pw[warp * kWinTile + j];
             const T* kr = tile + (long)j * RSP;
+            if (VW == 2) {
+                const uint32_t* k2 = reinterpret_cast<const uint32_t*>(kr);
 #pragma unroll
-            for (int i = 0; i < NI; i++) {
-                const int d = lane + 32 * i;
-                if (d < R) acc[i] = fmaf(w, to_f(kr[d]), acc[i]);
+                for (int i = 0; i < NI / 2; i++) {
+                    const int c = lane + 32 * i;              // column pair (2c, 2c + 1)
+                    if (2 * c < R) {
+                        const uint32_t u = k2[c];
+                        acc[2 * i] = fmaf(w, __uint_as_float(u << 16), acc[2 * i]);
+                        acc[2 * i + 1] = fmaf(w, __uint_as_float(u & 0xffff0000u), acc[2 * i + 1]);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < NI; i++) {
+                    const int d = lane + 32 * i;
+                    if (d < R) acc[i] = fmaf(w, to_f(kr[d]), acc[i]);
+                }
             }
         }
         __syncwarp();
@@ -139,42 +170,50 @@ __global__ void __launch_bounds__(kWinWarps * 32) latent_window_attn_kernel(cons
         if (lane == 0) { o[0] = m; o[1] = l; }
 #pragma unroll
         for (int i = 0; i < NI; i++) {
-            const int d = lane + 32 * i;
+            const int d = col(i);
             if (d < R) o[2 + d] = acc[i];
         }
     } else {
-        T* o = reinterpret_cast<T*>(p.out) + ((long)h * p.T + t) * R;
+        T* o = reinterpret_cast<T*>(p.out) + ((long)t * p.H + h) * R;
         const float inv = 1.0f / l;
 #pragma unroll
         for (int i = 0; i < NI; i++) {
-            const int d = lane + 32 * i;
+            const int d = col(i);
             if (d < R) o[d] = from_f<T>(acc[i] * inv);
         }
     }
 }
 
-// one warp per (token, head): fold the parts (those with sum 0 hold no key) and the sink
+// one CTA of 128 threads per (token, head): the parts' weights exp(m_s - m) / l once in shared memory (parts without a key
+// have m = -inf and weight 0), the sink in the denominator, then the columns in parallel
 template <typename T>
-__global__ void latent_window_merge_kernel(const WinAttnParams p) {
-    const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-    if (w >= p.T * p.H) return;
-    const int t = w / p.H, h = w % p.H, R = p.R;
+__global__ void __launch_bounds__(128) latent_window_merge_kernel(const WinAttnParams p) {
+    __shared__ float wgt[64];
+    __shared__ float red[4];
+    const int w = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int h = w % p.H, R = p.R;
     const float* part = p.part + (long)w * p.splits * (R + 2);
-    float m = p.sink ? p.sink[h] : -INFINITY;
-    for (int s = 0; s < p.splits; s++) m = fmaxf(m, part[(long)s * (R + 2)]);
-    float l = p.sink ? expf(p.sink[h] - m) : 0.f;
-    for (int s = 0; s < p.splits; s++) {
-        const float ms = part[(long)s * (R + 2)];
-        if (ms > -INFINITY) l += part[(long)s * (R + 2) + 1] * expf(ms - m);
-    }
-    T* o = reinterpret_cast<T*>(p.out) + ((long)h * p.T + t) * R;
-    for (int d = lane; d < R; d += 32) {
+    const float ms = tid < p.splits ? part[(long)tid * (R + 2)] : -INFINITY;        // splits <= 64
+    const float ls = tid < p.splits ? part[(long)tid * (R + 2) + 1] : 0.f;
+    float m = warp_max(ms);
+    if (lane == 0) red[warp] = m;
+    __syncthreads();
+    m = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    if (p.sink) m = fmaxf(m, p.sink[h]);
+    __syncthreads();
+    const float e = ms > -INFINITY ? expf(ms - m) : 0.f;
+    float l = warp_sum(ls * e);
+    if (lane == 0) red[warp] = l;
+    __syncthreads();
+    l = (red[0] + red[1]) + (red[2] + red[3]);
+    if (p.sink) l += expf(p.sink[h] - m);
+    if (tid < p.splits) wgt[tid] = e / l;
+    __syncthreads();
+    T* o = reinterpret_cast<T*>(p.out) + (long)w * R;
+    for (int d = tid; d < R; d += 128) {
         float a = 0.f;
-        for (int s = 0; s < p.splits; s++) {
-            const float ms = part[(long)s * (R + 2)];
-            if (ms > -INFINITY) a += part[(long)s * (R + 2) + 2 + d] * expf(ms - m);
-        }
-        o[d] = from_f<T>(a / l);
+        for (int s = 0; s < p.splits; s++) a = fmaf(wgt[s], part[(long)s * (R + 2) + 2 + d], a);
+        o[d] = from_f<T>(a);
     }
 }
 
@@ -185,7 +224,7 @@ static int launch_win(const WinAttnParams& p, size_t smem, cudaStream_t st) {
         if (smem > 48 * 1024) KTB_CUDA_CHECK(cudaFuncSetAttribute(latent_window_attn_kernel<T, NI, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         latent_window_attn_kernel<T, NI, true><<<grid, kWinWarps * 32, smem, st>>>(p);
         KTB_LAUNCH_CHECK();
-        latent_window_merge_kernel<T><<<(p.T * p.H * 32 + 255) / 256, 256, 0, st>>>(p);
+        latent_window_merge_kernel<T><<<p.T * p.H, 128, 0, st>>>(p);
         KTB_LAUNCH_CHECK();
     } else {
         if (smem > 48 * 1024) KTB_CUDA_CHECK(cudaFuncSetAttribute(latent_window_attn_kernel<T, NI, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -215,7 +254,7 @@ extern "C" int ktb200_latent_window_attn(const void* q, const void* q_abs, int n
                                          const float* sink, int window, const int* pos, const int* slot, const int* page_table, int max_pages, int page_size, const void* cache,
                                          void* out, int n_tokens, int splits, void* workspace, int dtype, void* stream) {
     if (!q || !q_abs || !pos || !slot || !page_table || !cache || !out || num_heads <= 0 || dim < 0 || rot_dim < 0 || kv_rank <= 0 || kv_rank > 1024 || rot_dims < 0 ||
-        rot_dims > rot_dim || (rot_dims & 1) || (rot_dims && !inv_freq) || max_pages <= 0 || page_size <= 0 || (splits > 1 && !workspace)) {
+        rot_dims > rot_dim || (rot_dims & 1) || (rot_dims && !inv_freq) || max_pages <= 0 || page_size <= 0 || (splits > 1 && !workspace) || splits > 64) {
         set_error("latent_window_attn: bad argument (latent size <= 1024)");
         return KTB200_EINVAL;
     }

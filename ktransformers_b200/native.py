@@ -111,6 +111,9 @@ SEQ_SYMBOLS = {
     "ktb200_latent_prep": (_I, [_VP, _L, _I, _I, _I, _I, _VP, _VP, _VP, _F, _VP, _VP, _VP, _I, _I, _VP, _VP, _I, _I, _VP]),
     "ktb200_latent_window_attn_workspace": (C.c_size_t, [_I, _I, _I, _I]),
     "ktb200_latent_window_attn": (_I, [_VP, _VP, _I, _I, _I, _I, _I, _VP, _F, _VP, _I, _VP, _VP, _VP, _I, _I, _VP, _VP, _I, _I, _VP, _I, _VP]),
+    "ktb200_latent_window_attn_tc_workspace": (C.c_size_t, [_I, _I, _I, _I]),
+    "ktb200_latent_window_attn_tc": (_I, [_VP, _VP, _I, _F, _VP, _I, _VP, _VP, _VP, _I, _I, _VP, _L, _VP, _I, _I, _VP, C.c_size_t, _VP]),
+    "ktb200_rope_rows": (_I, [_VP, _I, _I, _I, _I, _VP, _VP, _VP, _I, _I, _VP]),
     "ktb200_sigmoid_gate_mul": (_I, [_VP, _VP, _L, _VP, _I, _I, _I, _I, _VP]),
     "ktb200_poly_norm": (_I, [_VP, _VP, _VP, _F, _I, _I, _I, _VP]),
     "ktb200_experts_gate_up": (_I, [_VP, _VP, _I, _VP, _VP, _VP, _I, _I, _I, _I, _VP]),

@@ -102,12 +102,20 @@ class KLatentWindowAttention(torch.nn.Module):
         cq, c, k_r -> cache                                      ktb200_latent_prep (two RMS norms, rotation, paged write)
         q        = W_uq cq                                       GEMM
         qa_h     = W_uk,h^T q_h[:dim]                            batched GEMM (absorb)
-        lat_h    = sum_j softmax_sink(qa_h . c_j + rot(q_h[dim:]) . k_r,j) c_j     ktb200_latent_window_attn
+        lat_h    = sum_j softmax_sink(qa_h . c_j + rot(q_h[dim:]) . k_r,j) c_j     ktb200_latent_window_attn, or on tcgen05:
+                                                                 ktb200_rope_rows + ktb200_latent_window_attn_tc
         o_h      = W_uv,h lat_h                                  batched GEMM (absorb)
         out      = W_o (o * sigmoid(g))                          ktb200_sigmoid_gate_mul + GEMM
 
     Only c and k_r are cached (`kv_rank + rot_dim` values per token and layer).  Sizes, window, sink, scale and the rotation
-    constants are constructor parameters (models/configuration_lekapel.LatentAttentionSpec)."""
+    constants are constructor parameters (models/configuration_lekapel.LatentAttentionSpec).
+
+    Two attention kernels: with bf16, kv_rank 512, rot_dim 64 and pages that are a multiple of 32 tokens (DeepSeek's latent
+    sizes) the tcgen05 / TMEM / TMA kernel of MLA decode runs, one CTA per (token, 64 heads, key split), with the
+    probabilities split into two bf16 terms so that they keep fp32-like precision; any other size, and fp32, runs the
+    CUDA-core kernel of csrc/window_attn.cu."""
+
+    use_tensor_path = True
 
     def __init__(self, width: int, spec, eps: float, layer_idx: int, dtype=torch.bfloat16, device="cuda"):
         super().__init__()
@@ -155,18 +163,27 @@ class KLatentWindowAttention(torch.nn.Module):
                                                 self.kv_norm.data_ptr(), float(self.eps), batch.pos.data_ptr(), batch.slot.data_ptr(), cache.page_table.data_ptr(),
                                                 cache.max_pages_per_seq, cache.page_size, kv.data_ptr(), cq.data_ptr(), T, code, st))
         q = torch.nn.functional.linear(cq, self.uq)
-        if s.dim:
-            q_abs = torch.bmm(q.view(T, s.heads, s.dim + s.rot_dim)[:, :, : s.dim].transpose(0, 1), self.w_uk)
+        if s.dim:       # [H, T, R] out of the batched product, token-major for the attention kernels
+            q_abs = torch.bmm(q.view(T, s.heads, s.dim + s.rot_dim)[:, :, : s.dim].transpose(0, 1), self.w_uk).transpose(0, 1).contiguous()
         else:
-            q_abs = torch.zeros((s.heads, T, s.kv_rank), dtype=dt, device=dev)
-        lat = torch.empty((s.heads, T, s.kv_rank), dtype=dt, device=dev)
-        splits = self.pick_splits(T, batch.max_kv)
-        ws = torch.empty(lib.ktb200_latent_window_attn_workspace(T, s.heads, s.kv_rank, splits) // 4, dtype=torch.float32, device=dev) if splits > 1 else None
-        native.check_seq(lib.ktb200_latent_window_attn(q.data_ptr(), q_abs.data_ptr(), s.heads, s.dim, s.rot_dim, s.kv_rank, s.rot.dims, self.inv_freq.data_ptr(), float(s.scale),
-                                                       self.sink.data_ptr(), s.window or 0, batch.pos.data_ptr(), batch.slot.data_ptr(), cache.page_table.data_ptr(),
-                                                       cache.max_pages_per_seq, cache.page_size, kv.data_ptr(), lat.data_ptr(), T, splits,
-                                                       ws.data_ptr() if ws is not None else None, code, st))
-        o = torch.bmm(lat, self.w_uv_t)
+            q_abs = torch.zeros((T, s.heads, s.kv_rank), dtype=dt, device=dev)
+        lat = torch.empty((T, s.heads, s.kv_rank), dtype=dt, device=dev)
+        if self.use_tensor_path and dt == torch.bfloat16 and s.kv_rank == 512 and s.rot_dim == 64 and cache.page_size % 32 == 0:
+            q_rot = torch.empty((T, s.heads, s.rot_dim), dtype=dt, device=dev)
+            native.check_seq(lib.ktb200_rope_rows(q.data_ptr(), s.heads, s.dim, s.rot_dim, s.rot.dims, self.inv_freq.data_ptr(), batch.pos.data_ptr(), q_rot.data_ptr(), T, code, st))
+            wsb = lib.ktb200_latent_window_attn_tc_workspace(T, s.heads, s.window or 0, batch.max_kv)
+            ws = torch.empty(wsb // 4, dtype=torch.float32, device=dev)
+            native.check_seq(lib.ktb200_latent_window_attn_tc(q_abs.data_ptr(), q_rot.data_ptr(), s.heads, float(s.scale), self.sink.data_ptr(), s.window or 0, batch.pos.data_ptr(),
+                                                              batch.slot.data_ptr(), cache.page_table.data_ptr(), cache.max_pages_per_seq, cache.page_size, kv.data_ptr(),
+                                                              kv.shape[0] * kv.shape[1], lat.data_ptr(), T, batch.max_kv, ws.data_ptr(), wsb, st))
+        else:
+            splits = self.pick_splits(T, batch.max_kv)
+            ws = torch.empty(lib.ktb200_latent_window_attn_workspace(T, s.heads, s.kv_rank, splits) // 4, dtype=torch.float32, device=dev) if splits > 1 else None
+            native.check_seq(lib.ktb200_latent_window_attn(q.data_ptr(), q_abs.data_ptr(), s.heads, s.dim, s.rot_dim, s.kv_rank, s.rot.dims, self.inv_freq.data_ptr(),
+                                                           float(s.scale), self.sink.data_ptr(), s.window or 0, batch.pos.data_ptr(), batch.slot.data_ptr(),
+                                                           cache.page_table.data_ptr(), cache.max_pages_per_seq, cache.page_size, kv.data_ptr(), lat.data_ptr(), T, splits,
+                                                           ws.data_ptr() if ws is not None else None, code, st))
+        o = torch.bmm(lat.transpose(0, 1), self.w_uv_t)
         og = torch.empty((T, s.heads * s.vdim), dtype=dt, device=dev)
         native.check_seq(lib.ktb200_sigmoid_gate_mul(o.data_ptr(), proj[:, s.q_rank + s.kv_rank + s.rot_dim:].data_ptr(), self.n_in, og.data_ptr(), T, s.heads, s.vdim, code, st))
         return torch.nn.functional.linear(og, self.o)

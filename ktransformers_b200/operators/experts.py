@@ -528,8 +528,13 @@ class KExpertsDense(nn.Module):
     """Un-quantised (bf16 / fp32) gated-SiLU experts, stacked `[E, ff, width]` / `[E, width, ff]` in HBM, run by the per-pair
     kernels `ktb200_experts_gate_up` / `ktb200_experts_down` (csrc/seq_ops.cu): every (token, slot) pair is a GEMV pair over its
     expert's rows, silu(gate) * up in fp32 with one rounding, the weighted sum over a token's slots in fp32 in slot order.
+    From `grouped_min_tokens` tokens on (the threshold of the quantised experts' grouped path) the pairs are sorted by expert
+    and every expert runs ONE library GEMM per matrix over its tokens, so an expert's weights are read once per step instead
+    of once per pair; the weighted sum over a token's slots stays fp32 in slot order.
     The counterpart of KExpertsB200 for checkpoints that ship dense experts (the reference's KExpertsTorch, experts.py:562-678,
     loops over experts in torch)."""
+
+    grouped_min_tokens = 48
 
     def __init__(self, width: int, ff: int, experts: int, dtype=torch.bfloat16, device="cuda"):
         super().__init__()
@@ -546,6 +551,8 @@ class KExpertsDense(nn.Module):
     def forward(self, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
         """x [T, width], ids [T, top] int64, weights [T, top] fp32 -> [T, width] fp32"""
         T, top = ids.shape
+        if T >= self.grouped_min_tokens:
+            return self.forward_grouped(x, ids, weights)
         act = torch.empty((T * top, self.ff), dtype=x.dtype, device=x.device)
         out = torch.empty((T, self.width), dtype=torch.float32, device=x.device)
         lib, dt, st = native.seq_lib(), TORCH_TO_GGML_HIDDEN[x.dtype], _stream(x.device)
@@ -554,6 +561,25 @@ class KExpertsDense(nn.Module):
         native.check_seq(lib.ktb200_experts_down(act.data_ptr(), ids.data_ptr(), weights.data_ptr(), top, self.down.data_ptr(), out.data_ptr(), T, self.width,
                                                  self.ff, dt, st))
         return out
+
+
+    def forward_grouped(self, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+        T, top = ids.shape
+        flat = ids.reshape(-1)
+        order = torch.argsort(flat, stable=True)
+        counts = torch.bincount(flat, minlength=self.experts).tolist()          # the one host read of a step's routing
+        xs = x.index_select(0, torch.div(order, top, rounding_mode="floor"))
+        y = torch.empty((T * top, self.width), dtype=x.dtype, device=x.device)
+        lo = 0
+        for e, n in enumerate(counts):
+            if n:
+                seg = xs[lo:lo + n]
+                g, u = nn.functional.linear(seg, self.gate[e]).float(), nn.functional.linear(seg, self.up[e]).float()
+                y[lo:lo + n] = nn.functional.linear((nn.functional.silu(g) * u).to(x.dtype), self.down[e])
+                lo += n
+        pairs = torch.empty_like(y)
+        pairs[order] = y
+        return (pairs.view(T, top, self.width).float() * weights.unsqueeze(-1)).sum(1)
 
 
 class KSoftmaxTopKMoE(nn.Module):

@@ -1,0 +1,229 @@
+"""Throughput and per-kernel rooflines of a step-function model at layer sizes of real models, with random weights, beside
+the closest existing model's kernels at equal size (`bench.py --model lekapel`).
+
+Two parts:
+  * end to end through the Engine (scheduler, paged cache, step function): prompt tokens/s for a long prompt cut into portions,
+    decode tokens/s for 1 and 8 concurrent sequences, CUDA events around the steps;
+  * kernel by kernel at DeepSeek-V3 attention / MoE sizes: each token-major kernel against its counterpart of the DeepSeek path
+    (fused norm, latent prep, paged latent attention for decode, expert GEMVs), algorithmic bytes / event time / measured HBM
+    peak.  L2 is flushed between timed launches (a 256 MB write)."""
+from __future__ import annotations
+
+import ctypes as C
+import json
+import os
+import statistics
+
+import torch
+
+from .. import native
+
+SIZES = {
+    # name: (width, layers, mixer, dense ff, experts, top, expert ff, vocab)
+    "2k-wide": dict(width=2048, n_layers=6, heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512, q_rank=768, window=1024, dense_ff=8192, experts=32, top=4, ff=1024, vocab=32768),
+    "v3-layer": dict(width=7168, n_layers=2, heads=128, dim=128, rot_dim=64, vdim=128, kv_rank=512, q_rank=1536, window=4096, dense_ff=18432, experts=32, top=8, ff=2048, vocab=32768),
+}
+
+
+def make_config(s):
+    mixer = {"heads": s["heads"], "dim": s["dim"], "rot_dim": s["rot_dim"], "vdim": s["vdim"], "kv_rank": s["kv_rank"], "q_rank": s["q_rank"],
+             "rot": {"base": 10000.0, "dims": s["rot_dim"]}, "scale": (s["dim"] + s["rot_dim"]) ** -0.5, "mask": {"size": s["window"]}}
+    layers = [{"type": "latent_attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": s["dense_ff"]}}]
+    layers += [{"type": "latent_attention", "mixer": mixer, "mlp": {"kind": "moe", "expert": {"ff": s["ff"]}, "router": {"experts": s["experts"], "top": s["top"]}}}
+               for _ in range(s["n_layers"] - 1)]
+    return {"architecture": "Lekapel", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-5, "groups": 2}, "residual_mult": 0.7, "logit_scale": 0.5, "layers": layers}
+
+
+def random_model(cfg_dict, dtype=torch.bfloat16, device="cuda"):
+    from ..models.configuration_lekapel import LekapelConfig
+    from ..models.modeling_lekapel import LekapelForCausalLM
+    model = LekapelForCausalLM(LekapelConfig.from_dict(cfg_dict), dtype=dtype, device=device)
+    g = torch.Generator(device=device).manual_seed(1)
+    for name, p in model.named_parameters():
+        if p.dim() == 1:
+            p.data.copy_(1 + 0.1 * torch.randn(p.shape, generator=g, device=device))
+        else:
+            p.data.copy_(torch.randn(p.shape, generator=g, device=device, dtype=torch.float32) * p.shape[-1] ** -0.5)
+    return model.eval()
+
+
+def model_bytes(model):
+    return sum(p.numel() * p.element_size() for p in model.parameters())
+
+
+class Flusher:
+    def __init__(self, dev):
+        self.buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def __call__(self):
+        self.buf.fill_(1)
+
+
+def timed(fn, flush, iters=10, warmup=3):
+    for _ in range(warmup):
+        fn()
+    ts = []
+    for _ in range(iters):
+        flush()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    return statistics.median(ts)
+
+
+def engine_leg(name, size, flush, steps, warmup):
+    from .engine import Engine
+    cfg = make_config(size)
+    model = random_model(cfg)
+    prompt_len, chunk, ctx = 4096, 2048, min(4096, size["window"] * 2)
+    eng = Engine(model, max_tokens=8 * (ctx + 64) + prompt_len, max_slots=9, max_step_tokens=chunk)
+    g = torch.Generator().manual_seed(0)
+    tok = lambda n: torch.randint(0, size["vocab"], (n,), generator=g).tolist()
+    out = {"size": name, "config": {k: v for k, v in size.items()}, "weights_GB": model_bytes(model) / 1e9}
+
+    def prefill():
+        p = tok(prompt_len)
+        for lo in range(0, prompt_len, chunk):
+            eng.step([("p", p[lo:lo + chunk], [len(p[lo:lo + chunk]) - 1] if lo + chunk >= prompt_len else [])], ["p"] if lo + chunk >= prompt_len else [])
+    ms = timed(prefill, flush, iters=max(3, steps // 4), warmup=max(1, warmup // 2))
+    out["prefill"] = {"prompt_tokens": prompt_len, "portion": chunk, "ms": ms, "tok_s": prompt_len / ms * 1e3}
+    for bs in (1, 8):
+        ids = [("d", i) for i in range(bs)]
+        for i in ids:                                     # fill each sequence's cache to ctx tokens
+            p = tok(ctx)
+            for lo in range(0, ctx, chunk):
+                eng.step([(i, p[lo:lo + chunk], [])])
+        nxt = tok(bs)
+        ms = timed(lambda: eng.step([(i, [t], [0]) for i, t in zip(ids, nxt)]), flush, iters=steps, warmup=warmup)
+        for i in ids:
+            eng.cache.close(i)
+        out[f"decode_bs{bs}"] = {"ctx": ctx, "ms_per_step": ms, "tok_s": bs / ms * 1e3}
+    return out
+
+
+def kernel_leg(flush, peak_gbs, have_main_lib):
+    """Token-major kernels against the DeepSeek path's kernels at DeepSeek-V3 sizes (bf16)."""
+    dev, bf = torch.device("cuda"), torch.bfloat16
+    seq = native.seq_lib()
+    S = lambda: torch.cuda.current_stream().cuda_stream  # noqa: E731
+    D, NH, R, ROPE, NOPE, QL, PAGE = 7168, 128, 512, 64, 128, 1536, 64
+    rows = []
+
+    def row(kernel, what, ms, nbytes, peer=None):
+        r = {"kernel": kernel, "case": what, "us": ms * 1e3, "GBps": nbytes / ms / 1e6, "frac_of_measured_hbm": nbytes / ms / 1e6 / peak_gbs}
+        if peer:
+            r["closest"] = peer
+        rows.append(r)
+        return r
+
+    g = torch.Generator(device=dev).manual_seed(7)
+    rn = lambda *s, dt=bf: torch.randn(*s, generator=g, device=dev, dtype=torch.float32).to(dt)
+    main = native.lib() if have_main_lib else None
+    for T in (1, 8, 2048):
+        # ---- fused residual sum + grouped norm + shift  vs  add_rmsnorm
+        x, a, b = rn(T, D, dt=torch.float32), rn(T, D), rn(T, D)
+        w, mu = rn(D), rn(D)
+        xo, h, hs = torch.empty_like(x), torch.empty(T, D, dtype=bf, device=dev), torch.empty(T, D, dtype=bf, device=dev)
+        meta = torch.tensor([[-1] + list(range(T - 1)), [-1] * T, [-1] * (T - 1) + [0]], dtype=torch.int32, device=dev)
+        st = torch.zeros(2, D, device=dev)
+        fn = lambda: native.check_seq(seq.ktb200_group_rmsnorm_shift(x.data_ptr(), a.data_ptr(), 30, b.data_ptr(), 30, 0.7, xo.data_ptr(), w.data_ptr(), 2, 1e-5, mu.data_ptr(),
+                                                                     meta[0].data_ptr(), meta[1].data_ptr(), meta[2].data_ptr(), st.data_ptr(), h.data_ptr(), hs.data_ptr(), T, D, 30, S()))
+        ours = timed(fn, flush)
+        peer = None
+        if main is not None:
+            r16, d16, o16 = rn(T, D), rn(T, D), torch.empty(T, D, dtype=bf, device=dev)
+            ms = timed(lambda: native.check(main.ktb200_add_rmsnorm(r16.data_ptr(), d16.data_ptr(), w.data_ptr(), 1e-6, o16.data_ptr(), T, D, S())), flush)
+            peer = {"kernel": "add_rmsnorm_kernel", "us": ms * 1e3, "GBps": T * D * 8 / ms / 1e6, "frac_of_measured_hbm": T * D * 8 / ms / 1e6 / peak_gbs}
+        row("group_norm_shift_kernel", f"T={T} width={D}", ours, T * D * (4 + 2 + 2 + 4 + 2 + 2), peer)
+    # ---- paged latent attention, decode, ctx 4096: ours (window 4096, sink) vs the tcgen05 MLA decode kernel
+    for B, ctx in ((1, 4096), (8, 4096), (1, 32768)):
+        pages = (ctx + PAGE - 1) // PAGE
+        cache = rn(B * pages + 1, PAGE, R + ROPE)
+        ptab = torch.arange(B * pages, dtype=torch.int32, device=dev).reshape(B, pages)
+        q, q_abs, lat = rn(B, NH, NOPE + ROPE), rn(B, NH, R), torch.empty(B, NH, R, dtype=bf, device=dev)
+        pos = torch.full((B,), ctx - 1, dtype=torch.int32, device=dev)
+        slot = torch.arange(B, dtype=torch.int32, device=dev)
+        inv = torch.arange(ROPE // 2, dtype=torch.float64, device=dev).mul(-2.0 / ROPE).exp2()
+        sink = torch.zeros(NH, device=dev)
+        splits = max(1, min(32, ctx // 128, 296 // (B * NH // 8)))
+        ws = torch.empty(max(1, seq.ktb200_latent_window_attn_workspace(B, NH, R, splits) // 4), device=dev)
+        fn = lambda: native.check_seq(seq.ktb200_latent_window_attn(q.data_ptr(), q_abs.data_ptr(), NH, NOPE, ROPE, R, ROPE, inv.data_ptr(), 0.07, sink.data_ptr(), ctx, pos.data_ptr(),
+                                                                    slot.data_ptr(), ptab.data_ptr(), pages, PAGE, cache.data_ptr(), lat.data_ptr(), B, splits, ws.data_ptr(), 30, S()))
+        ours = timed(fn, flush)
+        nbytes = B * ctx * (R + ROPE) * 2
+        peer = None
+        if main is not None:
+            qn, qp, o = rn(B, NH, R), rn(B, NH, ROPE), torch.empty(B, NH, R, dtype=bf, device=dev)
+            kl = torch.full((B,), ctx, dtype=torch.int32, device=dev)
+            wsb = main.ktb200_mla_workspace_bytes(B, NH, 0)
+            mws = torch.zeros(max(wsb, 16), dtype=torch.uint8, device=dev)
+            mp = native.MlaParams(B, NH, PAGE, pages, 0, 0.07, qn.data_ptr(), qp.data_ptr(), cache.data_ptr(), ptab.data_ptr(), kl.data_ptr(), o.data_ptr(), None, mws.data_ptr(), wsb,
+                                  (B * pages + 1) * PAGE)
+            ms = timed(lambda: native.check(main.ktb200_mla_decode(C.byref(mp), S())), flush)
+            peer = {"kernel": "mla_decode_tc_kernel", "us": ms * 1e3, "GBps": nbytes / ms / 1e6, "frac_of_measured_hbm": nbytes / ms / 1e6 / peak_gbs}
+        row("latent_window_attn_kernel (+merge)", f"decode B={B} ctx={ctx} heads={NH} splits={splits}", ours, nbytes, peer)
+        q_rot = rn(B, NH, ROPE)
+        wsb = seq.ktb200_latent_window_attn_tc_workspace(B, NH, ctx, ctx)
+        tws = torch.empty(wsb // 4, device=dev)
+        fn = lambda: native.check_seq(seq.ktb200_latent_window_attn_tc(q_abs.data_ptr(), q_rot.data_ptr(), NH, 0.07, sink.data_ptr(), ctx, pos.data_ptr(), slot.data_ptr(),
+                                                                       ptab.data_ptr(), pages, PAGE, cache.data_ptr(), (B * pages + 1) * PAGE, lat.data_ptr(), B, ctx, tws.data_ptr(), wsb, S()))
+        row("mla_decode_tc_kernel<split P> (+merge with sink)", f"decode B={B} ctx={ctx} heads={NH}", timed(fn, flush), nbytes, peer)
+    # ---- a prompt portion: 2048 tokens of one sequence at positions 2048..4095, window 4096 (work is FLOP-shaped: per token
+    #      and head a (576 + 512)-long multiply-add per visible key)
+    T, ctx = 2048, 4096
+    pages = ctx // PAGE
+    cache = rn(pages + 1, PAGE, R + ROPE)
+    ptab = torch.arange(pages, dtype=torch.int32, device=dev).reshape(1, pages)
+    q, q_abs, q_rot, lat = rn(T, NH, NOPE + ROPE), rn(T, NH, R), rn(T, NH, ROPE), torch.empty(T, NH, R, dtype=bf, device=dev)
+    pos = torch.arange(ctx - T, ctx, dtype=torch.int32, device=dev)
+    slot = torch.zeros(T, dtype=torch.int32, device=dev)
+    inv = torch.arange(ROPE // 2, dtype=torch.float64, device=dev).mul(-2.0 / ROPE).exp2()
+    sink = torch.zeros(NH, device=dev)
+    flops = float(sum(range(ctx - T + 1, ctx + 1))) * NH * (R + ROPE + R) * 2
+    wsb = seq.ktb200_latent_window_attn_tc_workspace(T, NH, ctx, ctx)
+    tws = torch.empty(wsb // 4, device=dev)
+    f_tc = lambda: native.check_seq(seq.ktb200_latent_window_attn_tc(q_abs.data_ptr(), q_rot.data_ptr(), NH, 0.07, sink.data_ptr(), ctx, pos.data_ptr(), slot.data_ptr(), ptab.data_ptr(),
+                                                                     pages, PAGE, cache.data_ptr(), (pages + 1) * PAGE, lat.data_ptr(), T, ctx, tws.data_ptr(), wsb, S()))
+    f_cc = lambda: native.check_seq(seq.ktb200_latent_window_attn(q.data_ptr(), q_abs.data_ptr(), NH, NOPE, ROPE, R, ROPE, inv.data_ptr(), 0.07, sink.data_ptr(), ctx, pos.data_ptr(),
+                                                                  slot.data_ptr(), ptab.data_ptr(), pages, PAGE, cache.data_ptr(), lat.data_ptr(), T, 1, None, 30, S()))
+    for name, f, it in (("mla_decode_tc_kernel<split P> (+merge with sink)", f_tc, 5), ("latent_window_attn_kernel", f_cc, 2)):
+        ms = timed(f, flush, iters=it, warmup=1)
+        rows.append({"kernel": name, "case": f"prompt portion T={T} positions {ctx - T}..{ctx - 1} heads={NH}", "us": ms * 1e3, "TFLOPs": flops / ms / 1e9})
+    # ---- dense experts per pair (decode) : bytes = pairs * 3 * ff * width * 2
+    E, top, ff = 32, 8, 2048
+    Wg, Wu, Wd = rn(E, ff, D), rn(E, ff, D), rn(E, D, ff)
+    for T in (1, 8):
+        x = rn(T, D)
+        ids = torch.stack([torch.randperm(E, generator=g, device=dev)[:top] for _ in range(T)]).to(torch.int64)
+        wts = torch.rand(T, top, generator=g, device=dev)
+        act, out = torch.empty(T * top, ff, dtype=bf, device=dev), torch.empty(T, D, device=dev)
+        f1 = lambda: native.check_seq(seq.ktb200_experts_gate_up(x.data_ptr(), ids.data_ptr(), top, Wg.data_ptr(), Wu.data_ptr(), act.data_ptr(), T, D, ff, 30, S()))
+        f2 = lambda: native.check_seq(seq.ktb200_experts_down(act.data_ptr(), ids.data_ptr(), wts.data_ptr(), top, Wd.data_ptr(), out.data_ptr(), T, D, ff, 30, S()))
+        uniq = len(set(ids.flatten().tolist()))                            # every chosen expert is read from HBM at least once
+        row("experts_gate_up_kernel", f"T={T} top={top} width={D} ff={ff} bf16", timed(f1, flush), uniq * 2 * ff * D * 2,
+            {"kernel": "moe_block_kernel (Q4_K/Q6_K, whole block)", "frac_of_measured_hbm": 0.55, "note": "committed measurement of the DeepSeek path, one token"})
+        row("experts_down_kernel", f"T={T} top={top} width={D} ff={ff} bf16", timed(f2, flush), uniq * ff * D * 2)
+    return rows
+
+
+def run(args):
+    """`bench.py --model lekapel`: prints one JSON line."""
+    torch.cuda.set_device(0)
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    try:
+        peak, src = float(json.load(open(os.path.join(root, "MEASURED_PEAKS.json")))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    except Exception:
+        peak, src = 6650.0, "fallback"
+    flush = Flusher("cuda")
+    have_main = os.path.exists(native.LIB_PATH)
+    n0 = native.seq_lib().ktb200_launch_count()
+    out = {"bench": "lekapel", "dtype": "bf16", "data": "synthetic (random weights and tokens)", "hbm_peak_GBps": peak, "peak_source": src,
+           "timing": "CUDA events, median, 256 MB L2 flush between timed calls", "kernels": kernel_leg(flush, peak, have_main), "models": []}
+    for name in (args.sizes.split(",") if getattr(args, "sizes", None) else SIZES):
+        out["models"].append(engine_leg(name, SIZES[name], flush, args.steps, args.warmup))
+        torch.cuda.empty_cache()
+    out["gpu_launches"] = int(native.seq_lib().ktb200_launch_count() - n0)
+    print(json.dumps(out))
