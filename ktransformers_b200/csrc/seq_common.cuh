@@ -29,6 +29,22 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
+// four consecutive values (index a multiple of 4, rows 16- / 8-byte aligned) of an fp32 or bf16 array chosen at run time
+__device__ __forceinline__ float4 load4_hidden(const void* base, long idx, int type) {
+    if (type == KTB200_TYPE_BF16) {
+        const uint2 v = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(base) + idx);
+        return make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u), __uint_as_float(v.y << 16), __uint_as_float(v.y & 0xffff0000u));
+    }
+    return *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + idx);
+}
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) { return load4_hidden(p, 0, KTB200_TYPE_BF16); }
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+}
+
 // Partial dot product of a weight row with a vector held in shared memory (fp32), over the columns this lane owns.  Rows whose
 // byte length is a multiple of 16 (and 16-byte aligned) stream as 16-byte read-only loads; any other row element by element.
 __device__ __forceinline__ float lane_dot(const __nv_bfloat16* __restrict__ w, const float* __restrict__ xs, int n, int lane, bool vec) {

@@ -21,23 +21,26 @@
 namespace ktb {
 
 // ------------------------------------------------------------------------------------------------ norm + token shift
-// One CTA per token.  smem: inv[2][groups] | (stash) row[D] | prev row[D].  With `stash` the row (after the residual sum) and the
+// One CTA per token.  smem: inv[2][groups] (padded to 16 bytes) | (stash) row[D] | prev row[D].  With `stash` the row (after the residual sum) and the
 // previous token's row are read from global memory ONCE by all threads and kept in shared memory for the group sums and the
 // output pass; rows too wide for shared memory are re-read instead.
+constexpr int kNormBatch = 4;
 template <typename T>
 __global__ void __launch_bounds__(256) group_norm_shift_kernel(const float* __restrict__ x_in, const void* da, int a_type, const void* db, int b_type, float mult,
                                                                float* __restrict__ x_out, const T* __restrict__ w, int groups, float eps, const T* __restrict__ mu,
                                                                const int* __restrict__ prev_idx, const int* __restrict__ rd_row, const int* __restrict__ wr_row,
-                                                               float* __restrict__ state, T* __restrict__ h_out, T* __restrict__ hs_out, int D, int stash) {
+                                                               float* __restrict__ state, T* __restrict__ h_out, T* __restrict__ hs_out, int D, int stash, int vec) {
     extern __shared__ __align__(16) float sm[];
     float* inv_cur = sm;
     float* inv_prev = sm + groups;
-    float* cur = sm + 2 * groups;
+    float* cur = sm + ((2 * groups + 3) & ~3);      // 16-byte aligned: the staged rows are accessed as float4
     float* prv = cur + D;
     const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
     const int gs = D / groups;
     const bool add = da != nullptr || db != nullptr;
     const int pi = (mu && prev_idx) ? prev_idx[t] : -1;      // row of the previous token inside this step, or -1
+    const int rr = (mu && rd_row) ? rd_row[t] : -1;
+    const int wr = (mu && wr_row) ? wr_row[t] : -1;
     auto row_val = [&](int r, int i) -> float {
         float v = x_in[(long)r * D + i];
         if (add) {
@@ -48,13 +51,71 @@ __global__ void __launch_bounds__(256) group_norm_shift_kernel(const float* __re
         }
         return v;
     };
+    auto row_val4 = [&](int r, int i) -> float4 {
+        float4 v = load4(x_in + (long)r * D + i);
+        if (add) {
+            float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (da) { const float4 u = load4_hidden(da, (long)r * D + i, a_type); s.x += u.x; s.y += u.y; s.z += u.z; s.w += u.w; }
+            if (db) { const float4 u = load4_hidden(db, (long)r * D + i, b_type); s.x += u.x; s.y += u.y; s.z += u.z; s.w += u.w; }
+            v.x = v.x + mult * s.x; v.y = v.y + mult * s.y; v.z = v.z + mult * s.z; v.w = v.w + mult * s.w;
+        }
+        return v;
+    };
     if (stash) {
-        for (int i = tid; i < D; i += blockDim.x) {
-            cur[i] = row_val(t, i);
-            if (pi >= 0) prv[i] = row_val(pi, i);
+        if (vec) {      // kNormBatch independent 16-byte loads per array in flight before the first use
+            for (int base = 0; base < D; base += blockDim.x * 4 * kNormBatch) {
+                float4 v[kNormBatch], u[kNormBatch];
+#pragma unroll
+                for (int k = 0; k < kNormBatch; k++) {
+                    const int i = base + (k * blockDim.x + tid) * 4;
+                    if (i < D) {
+                        v[k] = row_val4(t, i);
+                        if (pi >= 0) u[k] = row_val4(pi, i);
+                    }
+                }
+#pragma unroll
+                for (int k = 0; k < kNormBatch; k++) {
+                    const int i = base + (k * blockDim.x + tid) * 4;
+                    if (i < D) {
+                        store4(cur + i, v[k]);
+                        if (pi >= 0) store4(prv + i, u[k]);
+                    }
+                }
+            }
+        } else {
+            for (int i = tid; i < D; i += blockDim.x) {
+                cur[i] = row_val(t, i);
+                if (pi >= 0) prv[i] = row_val(pi, i);
+            }
         }
         __syncthreads();
     }
+    if (stash && vec && nw % groups == 0 && gs % (4 * (nw / groups)) == 0) {
+        // every warp sums one of nw equal chunks (a group = nw / groups consecutive chunks); partial sums meet in shared memory
+        const int per = nw / groups, chunk = gs / per, g = warp / per;
+        const float* c = cur + g * gs + (warp % per) * chunk;
+        const float* q = prv + g * gs + (warp % per) * chunk;
+        float sc = 0.f, sp = 0.f;
+        for (int i = lane * 4; i < chunk; i += 128) {
+            const float4 v = load4(c + i);
+            sc += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+            if (pi >= 0) {
+                const float4 u = load4(q + i);
+                sp += (u.x * u.x + u.y * u.y) + (u.z * u.z + u.w * u.w);
+            }
+        }
+        sc = warp_sum(sc);
+        sp = warp_sum(sp);
+        float* part = prv + D;                     // [2][nw] behind the staged rows
+        if (lane == 0) { part[warp] = sc; part[nw + warp] = sp; }
+        __syncthreads();
+        if (warp == 0 && lane < groups) {
+            float a = 0.f, b = 0.f;
+            for (int k = 0; k < per; k++) { a += part[lane * per + k]; b += part[nw + lane * per + k]; }
+            inv_cur[lane] = 1.0f / sqrtf(a / (float)gs + eps);
+            inv_prev[lane] = 1.0f / sqrtf(b / (float)gs + eps);
+        }
+    } else
     for (int g = warp; g < groups; g += nw) {
         float sc = 0.f, sp = 0.f;
         for (int i = lane; i < gs; i += 32) {
@@ -73,8 +134,45 @@ __global__ void __launch_bounds__(256) group_norm_shift_kernel(const float* __re
         }
     }
     __syncthreads();
-    const int rr = (mu && rd_row) ? rd_row[t] : -1;
-    const int wr = (mu && wr_row) ? wr_row[t] : -1;
+    if (vec && stash) {     // four columns per thread and pass: one group, 16- / 8-byte loads and stores, loads batched
+        for (int base = 0; base < D; base += blockDim.x * 4 * kNormBatch) {
+            float4 wv[kNormBatch], mv[kNormBatch], sv[kNormBatch];
+#pragma unroll
+            for (int k = 0; k < kNormBatch; k++) {
+                const int i = base + (k * blockDim.x + tid) * 4;
+                if (i < D) {
+                    wv[k] = load4(w + i);
+                    if (mu) mv[k] = load4(mu + i);
+                    if (mu && pi < 0 && rr >= 0) sv[k] = load4(state + (long)rr * D + i);
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < kNormBatch; k++) {
+                const int i = base + (k * blockDim.x + tid) * 4;
+                if (i >= D) continue;
+                const float4 v = load4(cur + i);
+                if (add && x_out) store4(x_out + (long)t * D + i, v);
+                const float4 wi = wv[k];
+                const float ic = inv_cur[i / gs];
+                const float4 h = make_float4(v.x * ic * wi.x, v.y * ic * wi.y, v.z * ic * wi.z, v.w * ic * wi.w);
+                if (h_out) store4(h_out + (long)t * D + i, h);
+                if (mu) {
+                    float4 hp = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (pi >= 0) {
+                        const float4 u = load4(prv + i);
+                        const float ip = inv_prev[i / gs];
+                        hp = make_float4(u.x * ip * wi.x, u.y * ip * wi.y, u.z * ip * wi.z, u.w * ip * wi.w);
+                    } else if (rr >= 0) {
+                        hp = sv[k];
+                    }
+                    const float4 m4 = mv[k];
+                    if (hs_out) store4(hs_out + (long)t * D + i, make_float4(h.x + (hp.x - h.x) * m4.x, h.y + (hp.y - h.y) * m4.y, h.z + (hp.z - h.z) * m4.z, h.w + (hp.w - h.w) * m4.w));
+                    if (wr >= 0) store4(state + (long)wr * D + i, h);
+                }
+            }
+        }
+        return;
+    }
     for (int i = tid; i < D; i += blockDim.x) {
         const float v = stash ? cur[i] : row_val(t, i);
         if (add && x_out) x_out[(long)t * D + i] = v;
@@ -243,13 +341,17 @@ extern "C" int ktb200_group_rmsnorm_shift(const float* x_in, const void* delta_a
     if ((delta_a || delta_b) && (!x_out || x_out == x_in)) { set_error("group_rmsnorm_shift: the sum needs a separate output row buffer"); return KTB200_EINVAL; }
     if (shift && (!prev_idx || !rd_row || !wr_row || !state || !hs_out)) { set_error("group_rmsnorm_shift: shift needs its index rows, state and output"); return KTB200_EINVAL; }
     if (n_tokens == 0) return KTB200_OK;
-    size_t smem = 2 * (size_t)groups * sizeof(float);
-    const int stash = smem + 2 * (size_t)width * sizeof(float) <= 160 * 1024;
-    if (stash) smem += 2 * (size_t)width * sizeof(float);
+    size_t smem = (size_t)((2 * groups + 3) & ~3) * sizeof(float);
+    const int stash = smem + (2 * (size_t)width + 64) * sizeof(float) <= 160 * 1024;
+    if (stash) smem += (2 * (size_t)width + 64) * sizeof(float);      // two staged rows + the warps' partial sums
+    auto al = [](const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; };
+    const int vec = width % 4 == 0 && (width / groups) % 4 == 0 && al(x_in, 16) && al(x_out, 16) && al(delta_a, 16) && al(delta_b, 16) && al(weight, 16) && al(shift, 16) &&
+                    al(state, 16) && al(h_out, 16) && al(hs_out, 16);
     SEQ_DISPATCH(dtype, {
-        if (smem > 48 * 1024) KTB_CUDA_CHECK(cudaFuncSetAttribute(group_norm_shift_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        static size_t granted = 48 * 1024;      // opt-in shared memory, raised once per size
+        if (smem > granted) { KTB_CUDA_CHECK(cudaFuncSetAttribute(group_norm_shift_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); granted = smem; }
         group_norm_shift_kernel<T><<<n_tokens, 256, smem, (cudaStream_t)stream>>>(x_in, delta_a, a_type, delta_b, b_type, mult, x_out, (const T*)weight, groups, eps,
-                                                                                  (const T*)shift, prev_idx, rd_row, wr_row, state, (T*)h_out, (T*)hs_out, width, stash);
+                                                                                  (const T*)shift, prev_idx, rd_row, wr_row, state, (T*)h_out, (T*)hs_out, width, stash, vec);
     });
     KTB_LAUNCH_CHECK();
     return KTB200_OK;
@@ -310,7 +412,8 @@ extern "C" int ktb200_experts_gate_up(const void* x, const int64_t* ids, int top
     int ry = (ff + 7) / 8;   // row blocks: enough CTAs to fill 148 SMs several times over when there are few pairs
     { const int want = (148 * 8 + n_tokens * top - 1) / (n_tokens * top); if (ry > want) ry = want; if (ry < 1) ry = 1; }
     SEQ_DISPATCH(dtype, {
-        if (smem > 48 * 1024) KTB_CUDA_CHECK(cudaFuncSetAttribute(experts_gate_up_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        static size_t granted = 48 * 1024;
+        if (smem > granted) { KTB_CUDA_CHECK(cudaFuncSetAttribute(experts_gate_up_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); granted = smem; }
         experts_gate_up_kernel<T><<<dim3(n_tokens * top, ry), 256, smem, (cudaStream_t)stream>>>((const T*)x, ids, top, (const T*)w_gate, (const T*)w_up, (T*)act, width, ff);
     });
     KTB_LAUNCH_CHECK();
@@ -325,7 +428,8 @@ extern "C" int ktb200_experts_down(const void* act, const int64_t* ids, const fl
     int ry = (width + 7) / 8;
     { const int want = (148 * 8 + n_tokens - 1) / n_tokens; if (ry > want) ry = want; if (ry < 1) ry = 1; }
     SEQ_DISPATCH(dtype, {
-        if (smem > 48 * 1024) KTB_CUDA_CHECK(cudaFuncSetAttribute(experts_down_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        static size_t granted = 48 * 1024;
+        if (smem > granted) { KTB_CUDA_CHECK(cudaFuncSetAttribute(experts_down_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); granted = smem; }
         experts_down_kernel<T><<<dim3(n_tokens, ry), 256, smem, (cudaStream_t)stream>>>((const T*)act, ids, weights, top, (const T*)w_down, out, width, ff);
     });
     KTB_LAUNCH_CHECK();

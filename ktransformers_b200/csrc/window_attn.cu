@@ -221,13 +221,15 @@ template <typename T, int NI>
 static int launch_win(const WinAttnParams& p, size_t smem, cudaStream_t st) {
     const dim3 grid(p.T, (p.H + kWinWarps - 1) / kWinWarps, p.splits > 1 ? p.splits : 1);
     if (p.splits > 1) {
-        if (smem > 48 * 1024) KTB_CUDA_CHECK(cudaFuncSetAttribute(latent_window_attn_kernel<T, NI, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        static size_t granted = 48 * 1024;
+        if (smem > granted) { KTB_CUDA_CHECK(cudaFuncSetAttribute(latent_window_attn_kernel<T, NI, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); granted = smem; }
         latent_window_attn_kernel<T, NI, true><<<grid, kWinWarps * 32, smem, st>>>(p);
         KTB_LAUNCH_CHECK();
         latent_window_merge_kernel<T><<<p.T * p.H, 128, 0, st>>>(p);
         KTB_LAUNCH_CHECK();
     } else {
-        if (smem > 48 * 1024) KTB_CUDA_CHECK(cudaFuncSetAttribute(latent_window_attn_kernel<T, NI, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        static size_t granted = 48 * 1024;
+        if (smem > granted) { KTB_CUDA_CHECK(cudaFuncSetAttribute(latent_window_attn_kernel<T, NI, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); granted = smem; }
         latent_window_attn_kernel<T, NI, false><<<grid, kWinWarps * 32, smem, st>>>(p);
         KTB_LAUNCH_CHECK();
     }

@@ -529,8 +529,9 @@ class KExpertsDense(nn.Module):
     kernels `ktb200_experts_gate_up` / `ktb200_experts_down` (csrc/seq_ops.cu): every (token, slot) pair is a GEMV pair over its
     expert's rows, silu(gate) * up in fp32 with one rounding, the weighted sum over a token's slots in fp32 in slot order.
     From `grouped_min_tokens` tokens on (the threshold of the quantised experts' grouped path) the pairs are sorted by expert
-    and every expert runs ONE library GEMM per matrix over its tokens, so an expert's weights are read once per step instead
-    of once per pair; the weighted sum over a token's slots stays fp32 in slot order.
+    and each matrix runs as ONE library grouped GEMM over the per-expert token segments (bf16; fp32 and odd sizes: one GEMM
+    per expert), so an expert's weights are read once per step instead of once per pair; the weighted sum over a token's
+    slots stays fp32 in slot order.
     The counterpart of KExpertsB200 for checkpoints that ship dense experts (the reference's KExpertsTorch, experts.py:562-678,
     loops over experts in torch)."""
 
@@ -565,18 +566,25 @@ class KExpertsDense(nn.Module):
 
     def forward_grouped(self, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
         T, top = ids.shape
+        F = nn.functional
         flat = ids.reshape(-1)
         order = torch.argsort(flat, stable=True)
-        counts = torch.bincount(flat, minlength=self.experts).tolist()          # the one host read of a step's routing
+        counts = torch.bincount(flat, minlength=self.experts)
         xs = x.index_select(0, torch.div(order, top, rounding_mode="floor"))
-        y = torch.empty((T * top, self.width), dtype=x.dtype, device=x.device)
-        lo = 0
-        for e, n in enumerate(counts):
-            if n:
-                seg = xs[lo:lo + n]
-                g, u = nn.functional.linear(seg, self.gate[e]).float(), nn.functional.linear(seg, self.up[e]).float()
-                y[lo:lo + n] = nn.functional.linear((nn.functional.silu(g) * u).to(x.dtype), self.down[e])
-                lo += n
+        if x.dtype == torch.bfloat16 and self.width % 8 == 0 and self.ff % 8 == 0 and hasattr(F, "grouped_mm"):
+            # the library's grouped GEMM takes the segment ends on the device: no host read of the routing, three launches
+            offs = counts.cumsum(0).to(torch.int32)
+            g, u = F.grouped_mm(xs, self.gate.transpose(1, 2), offs=offs).float(), F.grouped_mm(xs, self.up.transpose(1, 2), offs=offs).float()
+            y = F.grouped_mm((F.silu(g) * u).to(x.dtype), self.down.transpose(1, 2), offs=offs)
+        else:
+            y = torch.empty((T * top, self.width), dtype=x.dtype, device=x.device)
+            lo = 0
+            for e, n in enumerate(counts.tolist()):                              # one host read of a step's routing
+                if n:
+                    seg = xs[lo:lo + n]
+                    g, u = F.linear(seg, self.gate[e]).float(), F.linear(seg, self.up[e]).float()
+                    y[lo:lo + n] = F.linear((F.silu(g) * u).to(x.dtype), self.down[e])
+                    lo += n
         pairs = torch.empty_like(y)
         pairs[order] = y
         return (pairs.view(T, top, self.width).float() * weights.unsqueeze(-1)).sum(1)

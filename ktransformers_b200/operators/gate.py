@@ -96,7 +96,11 @@ class KSoftmaxTopKGate(nn.Module):
     """Soft-max over all experts, the `top` largest kept with their scores as weights (no re-scaling): the router kernel's
     `scoring = softmax, topk_method = greedy, norm_topk_prob = 0, routed_scaling_factor = 1` case (DeepSeek-V2's gate,
     archive/ktransformers/models/modeling_deepseek.py:386-459), as a plain module for models that are built on the operators
-    directly.  Logits are an fp32 GEMV over fp32 router weights."""
+    directly.  Logits are an fp32 GEMV over fp32 router weights.  The kernel is built for decode-sized batches (one CTA row per
+    token); from `gemm_min_tokens` tokens the logits are one fp32 library GEMM (TF32 off) followed by torch's soft-max and
+    top-k, the way the reference's KMoEGate runs its torch gate (operators/gate.py:91-127)."""
+
+    gemm_min_tokens = 48
 
     def __init__(self, width: int, experts: int, top: int, device="cuda"):
         super().__init__()
@@ -108,6 +112,10 @@ class KSoftmaxTopKGate(nn.Module):
 
     def forward(self, x: torch.Tensor):
         n = x.shape[0]
+        if n >= self.gemm_min_tokens:
+            scores = torch.softmax(nn.functional.linear(x.float(), self.weight), dim=-1)
+            wt, idx = torch.topk(scores, self.top, dim=-1)
+            return idx, wt.contiguous()
         idx = torch.empty((n, self.top), dtype=torch.int64, device=x.device)
         wt = torch.empty((n, self.top), dtype=torch.float32, device=x.device)
         cfg = native.GateConfig(self.experts, self.width, self.top, 1, 1, _SCORING["softmax"], _TOPK["greedy"], 0, 1.0, self.weight.data_ptr(), None,
