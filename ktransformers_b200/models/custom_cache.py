@@ -193,8 +193,13 @@ class PagedStateCache:
             self.release_behind(s)
         self._touched.clear()
 
-    def build_batch(self, entries, want_all: bool = False) -> ForwardBatch:
-        """entries: [(seq_id, tokens, want)] — reserve pages, lay out the per-token index rows, one host-to-device copy."""
+    def capacity_per_sequence(self) -> int:
+        return self.max_pages_per_seq * self.page_size
+
+    def build_batch(self, entries, want_all: bool = False, static=None) -> ForwardBatch:
+        """entries: [(seq_id, tokens, want)] — reserve pages, lay out the per-token index rows, one host-to-device copy.
+        `static` = (meta [5, T] int32, tokens [T] int64) device buffers of a captured step: the rows are copied into them and
+        the batch is built on them, asking for every row (the caller picks the wanted ones from the captured output)."""
         rows, toks, want, base, max_kv = [[], [], [], [], []], [], [], 0, 0
         for seq_id, tokens, w in entries:
             s = self.open(seq_id)
@@ -211,6 +216,11 @@ class PagedStateCache:
             base += n
             max_kv = max(max_kv, start + n)
         self.sync_table()
+        if static is not None:
+            static[0].copy_(torch.tensor(rows, dtype=torch.int32))
+            static[1].copy_(torch.tensor(toks, dtype=torch.int64))
+            b = ForwardBatch(static[0], static[1], torch.tensor(want, dtype=torch.int64).to(self.device, non_blocking=True), self.capacity_per_sequence())
+            return b
         meta = torch.tensor(rows, dtype=torch.int32).to(self.device, non_blocking=True)
         return ForwardBatch(meta, torch.tensor(toks, dtype=torch.int64).to(self.device, non_blocking=True),
                             torch.tensor(want, dtype=torch.int64).to(self.device, non_blocking=True), max_kv)

@@ -43,22 +43,68 @@ class Sampler:
         return torch.multinomial(p, 1, generator=self.generator).squeeze(-1)
 
 
+class _CapturedStep:
+    """A decode step of a fixed batch size as a CUDA graph: static index / token buffers in, logits of every row out."""
+
+    def __init__(self, model, cache, n: int):
+        dev = cache.device
+        self.meta = torch.zeros((5, n), dtype=torch.int32, device=dev)
+        self.tokens = torch.zeros(n, dtype=torch.int64, device=dev)
+        self.all_rows = torch.arange(n, dtype=torch.int64, device=dev)
+        self.graph, self.logits = None, None
+
+    def capture(self, model, cache):
+        from ..models.custom_cache import ForwardBatch
+        batch = ForwardBatch(self.meta, self.tokens, self.all_rows, cache.capacity_per_sequence())
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.logits = model(batch, cache)
+
+
 class Engine:
-    def __init__(self, model, max_tokens: int = 8192, max_slots: int = 8, page_size: int = 64, max_step_tokens: int = 2048):
+    """`cuda_graphs`: steps in which every sequence brings exactly one token (decode) replay a captured graph per batch size
+    after two eager steps of that size (the launch-bound inner loop of generation); everything else runs eagerly."""
+
+    graph_max_batch = 47        # below the experts' and the router's switch to their prompt-sized paths
+
+    def __init__(self, model, max_tokens: int = 8192, max_slots: int = 8, page_size: int = 64, max_step_tokens: int = 2048, cuda_graphs: bool = True):
         self.model = model
         self.cache = model.make_cache(max_tokens, max_slots=max_slots, page_size=page_size)
         self.scheduler = Scheduler(self.cache, max_step_tokens=max_step_tokens)
+        self.cuda_graphs = cuda_graphs and self.cache.device.type == "cuda"
+        self._captured, self._seen = {}, {}
 
     @torch.no_grad()
     def step(self, entries: Sequence, end: Sequence = ()) -> torch.Tensor:
         """entries: (sequence id, tokens, wanted places among these tokens).  Sequences named in `end` give their pages, slot
         and state back after the step."""
+        n = len(entries)
+        if self.cuda_graphs and n <= self.graph_max_batch and all(len(e[1]) == 1 for e in entries):
+            self._seen[n] = self._seen.get(n, 0) + 1
+            if self._seen[n] > 2:
+                logits = self._replay(entries)
+                self.cache.commit()
+                for seq_id in end:
+                    self.cache.close(seq_id)
+                return logits
         batch = self.cache.build_batch(entries)
         logits = self.model(batch, self.cache)
         self.cache.commit()
         for seq_id in end:
             self.cache.close(seq_id)
         return logits
+
+    def _replay(self, entries) -> torch.Tensor:
+        n = len(entries)
+        step = self._captured.get(n)
+        if step is None:
+            step = self._captured[n] = _CapturedStep(self.model, self.cache, n)
+        batch = self.cache.build_batch(entries, static=(step.meta, step.tokens))
+        if step.graph is None:
+            torch.cuda.current_stream().synchronize()
+            step.capture(self.model, self.cache)
+        step.graph.replay()
+        return step.logits.index_select(0, batch.want)
 
     @torch.no_grad()
     def generate(self, prompts: List[List[int]], max_new_tokens: int, sampler: Optional[Sampler] = None, stop_token: Optional[int] = None) -> List[List[int]]:
