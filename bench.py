@@ -2,6 +2,7 @@
 """bench.py — decode tok/s of the quantized-MoE hot path at DeepSeek-V3 shapes.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+    python bench.py --model lekapel [--sizes 2k-wide,v3-layer]     (another workload: see ktransformers_b200/util/model_bench.py)
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
 Workload (config.workload): DeepSeek-V3 671B Q4_K_M single-stream decode, the MoE-block hot path of every
