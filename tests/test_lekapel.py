@@ -168,7 +168,7 @@ def test_sampler():
 # ------------------------------------------------------------------------------------------------ mechanisms alone (GPU)
 @gpu
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
-@pytest.mark.parametrize("groups,width", [(1, 20), (3, 36), (4, 256)])
+@pytest.mark.parametrize("groups,width", [(1, 20), (3, 36), (4, 256), (5, 35), (16, 64)])      # 16-byte and element-wise paths
 def test_group_norm_and_shift_kernel(dtype, tol, groups, width):
     from ktransformers_b200.models.custom_cache import PagedStateCache
     from ktransformers_b200.operators.norm import KGroupRMSNormShift
@@ -208,7 +208,7 @@ def test_poly_norm_mlp(dtype, tol):
 
 @gpu
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 3e-2)])
-@pytest.mark.parametrize("experts,top,ff,width", [(5, 2, 12, 24), (3, 1, 7, 20), (16, 4, 64, 128)])
+@pytest.mark.parametrize("experts,top,ff,width", [(5, 2, 12, 24), (3, 1, 7, 20), (16, 4, 64, 128), (4, 2, 6, 18)])
 @pytest.mark.parametrize("tokens", [11, 70])                 # per-pair kernels / pairs grouped by expert
 def test_softmax_topk_moe(dtype, tol, experts, top, ff, width, tokens):
     from ktransformers_b200.operators.experts import KSoftmaxTopKMoE
@@ -354,6 +354,18 @@ def test_other_sizes(tmp_path):
         eng, om = serve(tmp_path, cfg, "float32", seed=10 + k, max_tokens=64, max_slots=2, page_size=8)
         t = toks(30, cfg["vocab"], seed=k)
         assert rel(run_steps(eng, cut("a", t, [13, 2, 1]))["a"], oracle_logits(om, t)) < F32_TOL
+
+
+@gpu
+def test_captured_decode_steps_with_a_key_range_cut_for_a_large_cache(tmp_path):
+    """a roomy cache makes the replayed decode step cut its key range into many parts, most of them empty for a short sequence"""
+    cfg = U.config([(U.mixer(window=None, heads=3), U.moe()), (U.mixer(window=300, heads=2, kv_rank=40), U.dense(16))])
+    eng, om = serve(tmp_path, cfg, "float32", max_tokens=8192, max_slots=2, page_size=16)
+    for r, n in enumerate((40, 330)):
+        t = toks(n, seed=40 + r)
+        got = run_steps(eng, cut(("g", r), t, [n - 12] + [1] * 12))[("g", r)]
+        assert rel(got, oracle_logits(om, t)) < F32_TOL
+    assert 1 in eng._captured and eng._captured[1].graph is not None
 
 
 @gpu
