@@ -420,3 +420,37 @@ def test_greedy_generation_through_the_scheduler_and_the_command_line(tmp_path, 
     assert local_chat.main(args) == 0
     lines = [json.loads(l) for l in capsys.readouterr().out.strip().splitlines() if l.startswith("{")]
     assert [l["output"] for l in lines] == want[:2]
+
+
+@gpu
+@pytest.mark.parametrize("dtype,tol", [("float32", F32_TOL), ("bfloat16", BF16_TOL)])
+def test_trace_replay_runner(tmp_path, dtype, tol):
+    """bin/trace_run as a process: steps on standard input, one logits file per step that asks for some, `done <n>` lines"""
+    import os
+    import subprocess
+    import sys
+
+    import numpy as np
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = U.config(MIXED[:2], vocab=41)
+    w = U.weights(cfg, 5, torch.bfloat16 if dtype == "bfloat16" else torch.float32)
+    path = U.save(tmp_path / "m", cfg, w)
+    om = O.Model(cfg, w, torch.float64)
+    a, b = toks(21, 41, seed=1), toks(9, 41, seed=2)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:15], "want": [0, 14]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": a[15:17], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "a", "tokens": a[17:18], "want": [0]}], "end": []},
+             {"step": 3, "entries": [{"id": "a", "tokens": a[18:21], "want": [2, 1]}], "end": ["a"]},
+             {"step": 4, "entries": [{"id": "b", "tokens": b, "want": [8]}], "end": ["b"]}]
+    out = tmp_path / "out"
+    p = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", path, "--dtype", dtype, "--out", str(out), "--max-tokens", "64"],
+                       input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done ")] == [f"done {i}" for i in range(5)]
+    la, lb = oracle_logits(om, a), oracle_logits(om, b)
+    want = {0: la[[0, 14]], 2: la[[17]], 3: la[[20, 19]], 4: lb[[8]]}
+    assert not (out / "1.f32").exists()
+    err = rel if dtype == "float32" else rel_rows
+    for n, ref in want.items():
+        got = torch.from_numpy(np.fromfile(out / f"{n}.f32", dtype="<f4").reshape(-1, 41))
+        assert got.shape == ref.shape and err(got, ref) < tol
