@@ -313,12 +313,12 @@ __global__ void __launch_bounds__(256) experts_down_kernel(const T* __restrict__
     __syncthreads();
     const bool vec = rows_vectorise(Wd, F);
     for (int d = blockIdx.y * nw + warp; d < D; d += gridDim.y * nw) {
-        float acc = 0.f;
-        for (int j = 0; j < top; j++) {
+        float acc = 0.f;      // this lane's share of sum_j w_j * (row . act_j): ONE warp reduction per output row, and the
+        for (int j = 0; j < top; j++) {   // next expert's loads are not held up behind a shuffle chain
             const T* wd = Wd + (ids[t * top + j] * (long)D + d) * F;
-            float s = warp_sum(lane_dot(wd, as + j * F, F, lane, vec));
-            acc = fmaf(wts[t * top + j], s, acc);
+            acc = fmaf(wts[t * top + j], lane_dot(wd, as + j * F, F, lane, vec), acc);
         }
+        acc = warp_sum(acc);
         if (lane == 0) out[t * D + d] = acc;
     }
 }
