@@ -552,7 +552,8 @@ class KExpertsDense(nn.Module):
     def forward(self, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
         """x [T, width], ids [T, top] int64, weights [T, top] fp32 -> [T, width] fp32"""
         T, top = ids.shape
-        if T >= self.grouped_min_tokens:
+        fits = 4 * top * self.ff <= 200 * 1024 and 4 * self.width <= 200 * 1024      # the per-pair kernels stage these rows in shared memory
+        if T >= self.grouped_min_tokens or not fits:
             return self.forward_grouped(x, ids, weights)
         act = torch.empty((T * top, self.ff), dtype=x.dtype, device=x.device)
         out = torch.empty((T, self.width), dtype=torch.float32, device=x.device)
