@@ -16,7 +16,7 @@ One step = one token per GPU through the 58 layers.  N > 1: experts are sharded 
 (expert-parallel); per layer the N tokens are all-gathered, each GPU runs the (token, expert) pairs it owns
 and a reduce-scatter returns every token's combined output — value = N tokens / step time (weak scaling).
 
-Printed JSON line: see the task contract; `roofline` is for the dominant kernel (gate/up GEMV) from a live
+Printed JSON line: `roofline` is for the dominant kernel (gate/up GEMV) from a live
 CUDA-event pass, `cpu_baseline` / `--impl reference` time the reference's own CPU implementation
 (oracle/_ref, the unmodified llamafile MoE) on this box's host cores.
 """
@@ -40,7 +40,7 @@ N_GROUP, TOPK_GROUP, ROUTED_SCALE = 8, 4, 2.5
 Q4_K, Q6_K, BF16, F32 = 12, 14, 30, 0
 BYTES_GATE_UP_PER_EXPERT = 2 * I * H * 144 // 256           # 16,515,072
 BYTES_DOWN_PER_EXPERT = H * I * 210 // 256                  # 12,042,240
-BYTES_PER_EXPERT = BYTES_GATE_UP_PER_EXPERT + BYTES_DOWN_PER_EXPERT   # 28,557,312 (SURVEY §8d)
+BYTES_PER_EXPERT = BYTES_GATE_UP_PER_EXPERT + BYTES_DOWN_PER_EXPERT   # 28,557,312
 PREFILL_TOKENS = 1024   # the reference's group_max_len (experts.py:209): one chunk of MOE::forward_many
 
 

@@ -80,7 +80,7 @@ void ktb200_moe_destroy(ktb200_moe* moe);
 
 /* Replaces MOE::load_weights / load_weights_task (kt-kernel/ext_bindings.cpp:447-471).
  * Q6_K tensors are permuted IN PLACE, once, into the 16-byte-aligned "8-row SoA" layout that the
- * sm_100a kernels stream (DESIGN.md §3); other types are consumed as raw ggml blocks.
+ * sm_100a kernels stream; other types are consumed as raw ggml blocks.
  * Byte count is unchanged.  Idempotent per handle. */
 int ktb200_moe_load_weights(ktb200_moe* moe, void* stream);
 

@@ -17,7 +17,7 @@
 //     bank-conflict free without padding.  Q4_K rows need no re-tiling (144-byte blocks, 36-word stride).
 //
 // Arithmetic is unchanged from the earlier generations (bit-exact Q8_K activations, integer dot products, fp32
-// once per super-block): see DESIGN.md §2.
+// once per super-block).
 #pragma once
 #include "gemv_pipe.cuh"
 

@@ -2,7 +2,7 @@
 //
 // Replaces MLAWrapper.run / flashinfer BatchMLAPagedAttentionWrapper
 // (archive/ktransformers/operators/flashinfer_wrapper.py:117-161, attention.py:419-447) and the Triton split-KV decode
-// (archive/ktransformers/operators/triton_attention.py:16-385).  Math (attention.py:395-478, SURVEY Appendix A):
+// (archive/ktransformers/operators/triton_attention.py:16-385).  Math (attention.py:395-478):
 //     s[h,t] = (q_nope[h,:] . ckv[t,:] + q_pe[h,:] . k_pe[t,:]) * sm_scale        576-long dot, bf16 x bf16 -> fp32
 //     p      = softmax_t(s)   fp32, online; P is cast to bf16 before P.V            (triton_attention.py:137-141)
 //     out[h] = sum_t p[h,t] * ckv[t,:]                                             512 wide

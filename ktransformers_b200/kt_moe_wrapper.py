@@ -1,4 +1,4 @@
-"""`KTMoEWrapper` front door for the B200 experts (SURVEY §8f rank 1).
+"""`KTMoEWrapper` front door for the B200 experts.
 
 API mirror of kt-kernel's factory (kt-kernel/python/experts.py:72-262) and its inference base class
 (kt-kernel/python/experts_base.py:227-544): same constructor arguments, `load_weights(physical_to_logical_map_cpu)`,
@@ -42,7 +42,7 @@ class KTMoEWrapper:
                  numa_nodes: Optional[List[int]] = None, mode: str = "inference", device: str = "cuda",
                  key_template: str = "model.layers.{layer}.mlp.experts", dtype: torch.dtype = torch.bfloat16, **kwargs):
         if mode != "inference":
-            raise NotImplementedError("KTMoEWrapper (B200): only mode='inference' (SFT is out of scope, DESIGN.md §6)")
+            raise NotImplementedError("KTMoEWrapper (B200): only mode='inference' (SFT is out of scope)")
         if method not in B200_METHODS:
             raise NotImplementedError(f"Unsupported method: {method}. Supported methods: {sorted(B200_METHODS)}")
         if max_deferred_experts_per_token:

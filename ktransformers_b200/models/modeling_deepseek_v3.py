@@ -2,7 +2,7 @@
 
 Only the classes the hot path's YAML rules match against are defined here (the reference carries the
 whole HF model, archive/ktransformers/models/modeling_deepseek_v3.py; everything outside the MoE block
-is out of scope, SURVEY §2.2).  Semantics restate the reference:
+is out of scope).  Semantics restate the reference:
     DeepseekV3MLP   :385-397     down(silu(gate x) * up x)
     MoEGate         :400-481     sigmoid scoring + noaux_tc grouped top-k
     DeepseekV3MoE   :483-616     gate -> routed experts (+ shared experts)

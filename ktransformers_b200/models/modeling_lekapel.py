@@ -71,6 +71,19 @@ class LekapelForCausalLM(nn.Module):
         c = self.config
         return PagedStateCache(c.cache_row_widths(), c.width, max_tokens, max_slots, self.device, dtype=self.dtype, page_size=page_size, window=c.max_window())
 
+    def decode_is_capturable(self) -> bool:
+        """Whether a decode step makes no host read (then the engine may replay it as a CUDA graph): the per-pair expert kernels
+        never do; experts whose rows are too long for them do unless the library's grouped GEMM applies (bf16, sizes % 8)."""
+        for layer in self.layers:
+            e = getattr(layer.mlp, "experts", None)
+            if e is None:
+                continue
+            top = layer.mlp.router.top
+            fits = 4 * top * e.ff <= 200 * 1024 and 4 * e.width <= 200 * 1024
+            if not fits and not (self.dtype == torch.bfloat16 and e.width % 8 == 0 and e.ff % 8 == 0 and hasattr(F, "grouped_mm")):
+                return False
+        return True
+
     @torch.no_grad()
     def forward(self, batch: ForwardBatch, cache: PagedStateCache, residual_trace: Optional[List[torch.Tensor]] = None) -> torch.Tensor:
         """Runs the batch's tokens from the cache and state earlier steps left; returns fp32 logits [len(batch.want), vocab]."""

@@ -209,7 +209,7 @@ class KTB200Error(RuntimeError):
 
 
 def check(rc: int) -> None:
-    """Map C-ABI return codes onto the reference's Python-visible errors (SURVEY §8b error convention)."""
+    """Map C-ABI return codes onto the reference's Python-visible errors."""
     if rc == OK:
         return
     msg = lib().ktb200_last_error().decode(errors="replace")

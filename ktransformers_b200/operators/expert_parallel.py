@@ -1,4 +1,4 @@
-"""Expert-parallel dispatch/combine for decode (SURVEY §8e; spec: the HF EP branch of DeepseekV3MoE.moe_infer,
+"""Expert-parallel dispatch/combine for decode (spec: the HF EP branch of DeepseekV3MoE.moe_infer,
 archive/ktransformers/models/modeling_deepseek_v3.py:550-605, minus its host round trips).
 
 GPU g owns experts [g*E/N, (g+1)*E/N).  Every rank holds one (or a few) decode tokens.  Per MoE layer:

@@ -170,7 +170,7 @@ class KExpertsB200(KExpertsBase):
         x, ids, w = x.contiguous(), ids.contiguous(), w.contiguous()
         want = {0: torch.float32, 1: torch.float16, 30: torch.bfloat16}[self.hidden_type]
         if x.dtype != want:
-            # the reference silently mis-types here (SURVEY appendix A); take the dtype from the tensor instead
+            # the reference silently mis-types here; take the dtype from the tensor instead
             x = x.to(want)
         bsz_ptr = None
         if bsz_tensor is not None:

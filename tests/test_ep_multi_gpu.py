@@ -1,4 +1,4 @@
-"""Expert-parallel MoE block on real peer memory: needs >= 2 GPUs (skipped otherwise; run with `gpurun --gpus 2`)."""
+"""Expert-parallel MoE block on real peer memory: needs >= 2 GPUs (skipped otherwise)."""
 import os
 import subprocess
 import sys

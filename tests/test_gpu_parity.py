@@ -744,7 +744,7 @@ def test_moe_grouped_matches_per_pair_kernels():
 
 @pytest.mark.parametrize("qlen", [16, 64, 4096])
 def test_moe_grouped_vs_compiled_reference_forward_many(ref, qlen):
-    """VERDICT r1 item 6: against the UNMODIFIED reference's MOE::forward_many (oracle/_ref, moe.cpp:248-365; it takes over from
+    """Against the UNMODIFIED reference's MOE::forward_many (oracle/_ref, moe.cpp:248-365; it takes over from
     forward_one at group_min_len = 10) at qlen 16 (per-pair kernels here), 64 and 4096 (grouped path; four 1024-token chunks here,
     group_max_len 4096 there).  fp32 hidden: same tolerance as the decode path."""
     E, k, H, I = 8, 4, 1024, 512

@@ -369,6 +369,19 @@ def test_captured_decode_steps_with_a_key_range_cut_for_a_large_cache(tmp_path):
 
 
 @gpu
+def test_long_expert_rows_decode_without_capture(tmp_path):
+    """top x ff floats beyond the per-pair kernels' shared memory: decode takes the grouped path, which reads the routing counts
+    on the host in fp32, so the engine does not replay such a model's decode steps as graphs; the results still agree"""
+    cfg = U.config([(U.mixer(), U.moe(ff=6600, experts=9, top=8))], width=16, groups=2)
+    eng, om = serve(tmp_path, cfg, "float32", max_tokens=64, max_slots=2)
+    assert not eng.model.decode_is_capturable() and not eng.cuda_graphs
+    t = toks(14, seed=5)
+    got = run_steps(eng, cut("x", t, [6] + [1] * 8))["x"]
+    assert rel(got, oracle_logits(om, t)) < F32_TOL
+    assert not eng._captured
+
+
+@gpu
 def test_unequal_requests_in_one_batch_equal_each_alone(tmp_path):
     cfg = U.config(MIXED)
     eng, om = serve(tmp_path, cfg, "float32", max_tokens=256, max_slots=4, page_size=4)
