@@ -357,6 +357,31 @@ def test_other_sizes(tmp_path):
 
 
 @gpu
+@pytest.mark.parametrize("seed", range(8))
+def test_drawn_configurations(tmp_path, seed):
+    """sizes, layer order and constants drawn per seed (odd sizes, head counts that are no multiple of 8, windows around 32 and
+    64, experts with top from 1 to all): one prompt whole, in uneven portions, and with a decoded tail"""
+    import random
+    r = random.Random(seed)
+    width = r.choice([16, 40, 136, 320])
+    layers = []
+    for _ in range(r.randint(1, 4)):
+        rot_dim = r.choice([2, 6, 8, 16, 32])
+        m = U.mixer(heads=r.choice([1, 2, 5, 8, 12, 20]), dim=r.choice([4, 7, 24, 64]), rot_dim=rot_dim, vdim=r.choice([5, 8, 48]),
+                    kv_rank=r.choice([8, 33, 130, 256]), q_rank=r.choice([8, 12, 80]), window=r.choice([1, 2, 9, 31, 32, 33, 64, 65, None]),
+                    base=r.choice([100.0, 1e6]), rot_dims=r.choice([rot_dim, max(2, rot_dim // 4 * 2)]), scale=r.choice([None, 0.125]))
+        e = r.choice([2, 3, 17, 32])
+        layers.append((m, r.choice([None, U.dense(ff=r.choice([8, 100, 1030])), U.moe(ff=r.choice([4, 12, 96]), experts=e, top=r.randint(1, min(e, 8)))])))
+    cfg = U.config(layers, vocab=r.choice([31, 77, 1000]), width=width, groups=r.choice([1, 2, 4, 8]), eps=r.choice([1e-5, 1e-3]),
+                   residual_mult=r.choice([1.0, 0.3]), logit_scale=r.choice([1.0, 2.0]))
+    eng, om = serve(tmp_path, cfg, "float32", seed=seed, max_tokens=256, max_slots=2, page_size=r.choice([4, 16, 64]))
+    t = toks(r.choice([40, 90, 150]), cfg["vocab"], seed=seed)
+    want = oracle_logits(om, t)
+    for k, sizes in enumerate(([len(t)], [3, 17, 2, 1, 33, 2, 64], [len(t) - 20] + [1] * 20)):
+        assert rel(run_steps(eng, cut(("d", k), t, sizes))[("d", k)], want) < F32_TOL
+
+
+@gpu
 def test_captured_decode_steps_with_a_key_range_cut_for_a_large_cache(tmp_path):
     """a roomy cache makes the replayed decode step cut its key range into many parts, most of them empty for a short sequence"""
     cfg = U.config([(U.mixer(window=None, heads=3), U.moe()), (U.mixer(window=300, heads=2, kv_rank=40), U.dense(16))])
