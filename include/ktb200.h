@@ -397,6 +397,13 @@ int ktb200_experts_gate_up(const void* x, const int64_t* ids, int top, const voi
                            int width, int ff, int dtype, void* stream);
 int ktb200_experts_down(const void* act, const int64_t* ids, const float* weights, int top, const void* w_down, float* out, int n_tokens,
                         int width, int ff, int dtype, void* stream);
+/* the same for batches of a few tokens, by expert: each expert's rows are streamed once per `staged` (2 or 4; 0: chosen from the
+ *   batch) pairs routed to it instead of once per pair; pair_rows [T*top][width] fp32 is scratch for the per-pair down rows
+ *   before the weighted sum in slot order. */
+int ktb200_experts_gate_up_by_expert(const void* x, const int64_t* ids, int top, int n_experts, const void* w_gate, const void* w_up, void* act,
+                                     int n_tokens, int width, int ff, int staged, int dtype, void* stream);
+int ktb200_experts_down_by_expert(const void* act, const int64_t* ids, const float* weights, int top, int n_experts, const void* w_down,
+                                  float* pair_rows, float* out, int n_tokens, int width, int ff, int staged, int dtype, void* stream);
 
 /* Diagnostics (bench.py --probe): time a plain read-only stream over `bytes` of device memory.
  * mode 0 = grid-stride coalesced 16-byte loads; mode 1 = every warp reads chunk_bytes pieces at hashed offsets

@@ -323,6 +323,224 @@ __global__ void __launch_bounds__(256) experts_down_kernel(const T* __restrict__
     }
 }
 
+// ------------------------------------------------------------------------------------------------ dense experts, by expert
+// Batches of a few tokens: grid (experts, row blocks).  A CTA lists the pairs routed to ITS expert from the id array (in pair
+// order, so the result does not depend on the schedule), stages the rows of up to NT (2 or 4) of them in shared memory in
+// the operand type, and applies every weight row it streams to all of them: an expert's weights cross HBM once per
+// NT pairs instead of once per pair.  Per pair the products are summed in the order of the per-pair kernels.
+
+// pairs p (ascending) with ids[p] == e into list[0..n), n into list[P]; all threads of the CTA call it
+__device__ __forceinline__ int list_pairs_of_expert(const int64_t* __restrict__ ids, int P, int e, int* list) {
+    const int lane = threadIdx.x & 31;
+    if (threadIdx.x < 32) {
+        int n = 0;
+        for (int base = 0; base < P; base += 32) {
+            const int p = base + lane;
+            const bool hit = p < P && ids[p] == e;
+            const unsigned m = __ballot_sync(0xffffffffu, hit);
+            if (hit) list[n + __popc(m & ((1u << lane) - 1u))] = p;
+            n += __popc(m);
+        }
+        if (lane == 0) list[P] = n;
+    }
+    __syncthreads();
+    return list[P];
+}
+
+template <typename T> __device__ __forceinline__ void stage_rows(T* dst, const T* __restrict__ src, const int* rows, int div, int m, int n, bool vec) {
+    for (int k = 0; k < m; k++) {
+        const T* s = src + (long)(rows[k] / div) * n;
+        if (vec) {
+            constexpr int per = 16 / sizeof(T);
+            for (int i = threadIdx.x * per; i < n; i += blockDim.x * per) *reinterpret_cast<uint4*>(dst + (long)k * n + i) = *reinterpret_cast<const uint4*>(s + i);
+        } else {
+            for (int i = threadIdx.x; i < n; i += blockDim.x) dst[(long)k * n + i] = s[i];
+        }
+    }
+}
+
+// s[q][k] += w[q] . xs[k] for k < m, this lane's share: NW weight rows against the same staged rows (each staged value is
+// read from shared memory once for all of them, and NW 16-byte loads are in flight per lane)
+template <int NT, int NW>
+__device__ __forceinline__ void lane_dot_rows(const __nv_bfloat16* const (&w)[NW], const __nv_bfloat16* xs, int n, int m, int lane, bool vec, float (&s)[NW][NT]) {
+    if (vec) {
+        for (int i = lane * 8; i < n; i += 256) {
+            uint4 v[NW];
+#pragma unroll
+            for (int q = 0; q < NW; q++) v[q] = ldg_stream16(w[q] + i);
+#pragma unroll
+            for (int k = 0; k < NT; k++) {
+                if (k < m) {
+                    const uint4 a = *reinterpret_cast<const uint4*>(xs + (long)k * n + i);
+                    const float a0 = __uint_as_float(a.x << 16), a1 = __uint_as_float(a.x & 0xffff0000u), a2 = __uint_as_float(a.y << 16), a3 = __uint_as_float(a.y & 0xffff0000u);
+                    const float a4 = __uint_as_float(a.z << 16), a5 = __uint_as_float(a.z & 0xffff0000u), a6 = __uint_as_float(a.w << 16), a7 = __uint_as_float(a.w & 0xffff0000u);
+#pragma unroll
+                    for (int q = 0; q < NW; q++) {
+                        float t = s[q][k];
+                        t = fmaf(__uint_as_float(v[q].x << 16), a0, t);
+                        t = fmaf(__uint_as_float(v[q].x & 0xffff0000u), a1, t);
+                        t = fmaf(__uint_as_float(v[q].y << 16), a2, t);
+                        t = fmaf(__uint_as_float(v[q].y & 0xffff0000u), a3, t);
+                        t = fmaf(__uint_as_float(v[q].z << 16), a4, t);
+                        t = fmaf(__uint_as_float(v[q].z & 0xffff0000u), a5, t);
+                        t = fmaf(__uint_as_float(v[q].w << 16), a6, t);
+                        t = fmaf(__uint_as_float(v[q].w & 0xffff0000u), a7, t);
+                        s[q][k] = t;
+                    }
+                }
+            }
+        }
+    } else {
+        for (int i = lane; i < n; i += 32) {
+            float wv[NW];
+#pragma unroll
+            for (int q = 0; q < NW; q++) wv[q] = __bfloat162float(w[q][i]);
+#pragma unroll
+            for (int k = 0; k < NT; k++) {
+                if (k < m) {
+                    const float xv = __bfloat162float(xs[(long)k * n + i]);
+#pragma unroll
+                    for (int q = 0; q < NW; q++) s[q][k] = fmaf(wv[q], xv, s[q][k]);
+                }
+            }
+        }
+    }
+}
+template <int NT, int NW>
+__device__ __forceinline__ void lane_dot_rows(const float* const (&w)[NW], const float* xs, int n, int m, int lane, bool vec, float (&s)[NW][NT]) {
+    if (vec) {
+        for (int i = lane * 4; i < n; i += 128) {
+            uint4 v[NW];
+#pragma unroll
+            for (int q = 0; q < NW; q++) v[q] = ldg_stream16(w[q] + i);
+#pragma unroll
+            for (int k = 0; k < NT; k++) {
+                if (k < m) {
+                    const float4 a = *reinterpret_cast<const float4*>(xs + (long)k * n + i);
+#pragma unroll
+                    for (int q = 0; q < NW; q++) {
+                        float t = s[q][k];
+                        t = fmaf(__uint_as_float(v[q].x), a.x, t);
+                        t = fmaf(__uint_as_float(v[q].y), a.y, t);
+                        t = fmaf(__uint_as_float(v[q].z), a.z, t);
+                        t = fmaf(__uint_as_float(v[q].w), a.w, t);
+                        s[q][k] = t;
+                    }
+                }
+            }
+        }
+    } else {
+        for (int i = lane; i < n; i += 32) {
+            float wv[NW];
+#pragma unroll
+            for (int q = 0; q < NW; q++) wv[q] = w[q][i];
+#pragma unroll
+            for (int k = 0; k < NT; k++) {
+                if (k < m) {
+                    const float xv = xs[(long)k * n + i];
+#pragma unroll
+                    for (int q = 0; q < NW; q++) s[q][k] = fmaf(wv[q], xv, s[q][k]);
+                }
+            }
+        }
+    }
+}
+
+// shared memory: list[P + 1] ints (padded to 16 bytes) | rows [NT][D] of T.  A warp takes two ff rows at a time (gate and up of each).
+template <typename T, int NT>
+__global__ void __launch_bounds__(256) experts_gate_up_by_expert_kernel(const T* __restrict__ x, const int64_t* __restrict__ ids, int top, int P, const T* __restrict__ Wg,
+                                                                        const T* __restrict__ Wu, T* __restrict__ act, int D, int F) {
+    extern __shared__ __align__(16) unsigned char sm_raw[];
+    int* list = reinterpret_cast<int*>(sm_raw);
+    T* xs = reinterpret_cast<T*>(sm_raw + (((size_t)(P + 1) * sizeof(int) + 15) & ~(size_t)15));
+    const int e = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int n = list_pairs_of_expert(ids, P, e, list);
+    if (n == 0) return;
+    const T* g = Wg + (long)e * F * D;
+    const T* u = Wu + (long)e * F * D;
+    const bool vec = rows_vectorise(Wg, D) && rows_vectorise(Wu, D) && rows_vectorise(x, D);
+    for (int c = 0; c < n; c += NT) {
+        const int m = n - c < NT ? n - c : NT;
+        if (c) __syncthreads();      // the rows of the previous pairs are consumed
+        stage_rows(xs, x, list + c, top, m, D, vec);
+        __syncthreads();
+        for (int r = (blockIdx.y * nw + warp) * 2; r < F; r += gridDim.y * nw * 2) {
+            const int r1 = r + 1 < F ? r + 1 : r;      // an odd last row is done twice and stored once
+            const T* const w[4] = {g + (long)r * D, u + (long)r * D, g + (long)r1 * D, u + (long)r1 * D};
+            float s[4][NT];
+#pragma unroll
+            for (int q = 0; q < 4; q++)
+#pragma unroll
+                for (int k = 0; k < NT; k++) s[q][k] = 0.f;
+            lane_dot_rows<NT, 4>(w, xs, D, m, lane, vec, s);
+#pragma unroll
+            for (int k = 0; k < NT; k++) {
+                if (k < m) {
+                    const float a0 = warp_sum(s[0][k]), b0 = warp_sum(s[1][k]), a1 = warp_sum(s[2][k]), b1 = warp_sum(s[3][k]);
+                    if (lane == 0) {
+                        T* o = act + (long)list[c + k] * F;
+                        o[r] = from_f<T>(act_silu(a0) * b0);
+                        if (r1 != r) o[r1] = from_f<T>(act_silu(a1) * b1);
+                    }
+                }
+            }
+        }
+    }
+}
+
+// y[p][d] = Wd[ids[p]][d] . act[p]  (fp32, one row per pair); shared memory: list | rows [NT][F] of T.  A warp takes four rows at a time.
+template <typename T, int NT>
+__global__ void __launch_bounds__(256) experts_down_by_expert_kernel(const T* __restrict__ act, const int64_t* __restrict__ ids, int P, const T* __restrict__ Wd,
+                                                                     float* __restrict__ y, int D, int F) {
+    extern __shared__ __align__(16) unsigned char sm_raw[];
+    int* list = reinterpret_cast<int*>(sm_raw);
+    T* as = reinterpret_cast<T*>(sm_raw + (((size_t)(P + 1) * sizeof(int) + 15) & ~(size_t)15));
+    const int e = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int n = list_pairs_of_expert(ids, P, e, list);
+    if (n == 0) return;
+    const T* wd = Wd + (long)e * D * F;
+    const bool vec = rows_vectorise(Wd, F) && rows_vectorise(act, F);
+    for (int c = 0; c < n; c += NT) {
+        const int m = n - c < NT ? n - c : NT;
+        if (c) __syncthreads();
+        stage_rows(as, act, list + c, 1, m, F, vec);
+        __syncthreads();
+        for (int d = (blockIdx.y * nw + warp) * 4; d < D; d += gridDim.y * nw * 4) {
+            const T* w[4];
+#pragma unroll
+            for (int q = 0; q < 4; q++) w[q] = wd + (long)(d + q < D ? d + q : d) * F;
+            const T* const wc[4] = {w[0], w[1], w[2], w[3]};
+            float s[4][NT];
+#pragma unroll
+            for (int q = 0; q < 4; q++)
+#pragma unroll
+                for (int k = 0; k < NT; k++) s[q][k] = 0.f;
+            lane_dot_rows<NT, 4>(wc, as, F, m, lane, vec, s);
+#pragma unroll
+            for (int k = 0; k < NT; k++) {
+                if (k < m) {
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        const float a = warp_sum(s[q][k]);
+                        if (lane == q && d + q < D) y[(long)list[c + k] * D + d + q] = a;
+                    }
+                }
+            }
+        }
+    }
+}
+
+// out[t][d] = sum_j w[t][j] * y[t * top + j][d], fp32, slot order
+__global__ void __launch_bounds__(256) experts_combine_kernel(const float* __restrict__ y, const float* __restrict__ wts, int top, float* __restrict__ out, long n, int D) {
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+        const long t = i / D;
+        const int d = (int)(i - t * D);
+        float acc = 0.f;
+        for (int j = 0; j < top; j++) acc = fmaf(wts[t * top + j], y[(t * top + j) * D + d], acc);
+        out[i] = acc;
+    }
+}
+
 }  // namespace ktb
 
 using namespace ktb;
@@ -432,6 +650,65 @@ extern "C" int ktb200_experts_down(const void* act, const int64_t* ids, const fl
         if (smem > granted) { KTB_CUDA_CHECK(cudaFuncSetAttribute(experts_down_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); granted = smem; }
         experts_down_kernel<T><<<dim3(n_tokens, ry), 256, smem, (cudaStream_t)stream>>>((const T*)act, ids, weights, top, (const T*)w_down, out, width, ff);
     });
+    KTB_LAUNCH_CHECK();
+    return KTB200_OK;
+}
+
+static size_t by_expert_smem(int pairs, int staged, size_t row_bytes) { return (((size_t)(pairs + 1) * sizeof(int) + 15) & ~(size_t)15) + staged * row_bytes; }
+static int by_expert_row_blocks(int rows, int rows_per_warp, int pairs, int n_experts) {      // enough CTAs to fill 148 SMs several times over with the experts that can be active
+    const int active = pairs < n_experts ? pairs : n_experts;
+    int ry = (rows + 8 * rows_per_warp - 1) / (8 * rows_per_warp);
+    const int want = (148 * 8 + active - 1) / active;
+    if (ry > want) ry = want;
+    return ry < 1 ? 1 : ry;
+}
+// pairs staged per pass: 4 once there are as many pairs as experts (several pairs per expert become likely), else 2 (smaller CTAs, more of them per SM)
+static int by_expert_staged(int staged, int pairs, int n_experts) { return staged == 2 || staged == 4 ? staged : (pairs >= n_experts ? 4 : 2); }
+
+#define BY_EXPERT_LAUNCH(kernel, rows, rows_per_warp, row_bytes, ...)                                                                                     \
+    SEQ_DISPATCH(dtype, {                                                                                                                                  \
+        const size_t smem = by_expert_smem(P, NT, (row_bytes) * sizeof(T));                                                                                \
+        if (smem > 200 * 1024) { set_error(#kernel ": rows too long for shared memory"); return KTB200_EINVAL; }                                           \
+        static size_t granted = 48 * 1024;                                                                                                                 \
+        if (smem > granted) { KTB_CUDA_CHECK(cudaFuncSetAttribute(kernel<T, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); granted = smem; } \
+        kernel<T, NT><<<dim3(n_experts, by_expert_row_blocks(rows, rows_per_warp, P, n_experts)), 256, smem, (cudaStream_t)stream>>>(__VA_ARGS__);         \
+    })
+
+extern "C" int ktb200_experts_gate_up_by_expert(const void* x, const int64_t* ids, int top, int n_experts, const void* w_gate, const void* w_up, void* act, int n_tokens, int width,
+                                                int ff, int staged, int dtype, void* stream) {
+    if (!x || !ids || !w_gate || !w_up || !act || top <= 0 || n_experts <= 0 || width <= 0 || ff <= 0) { set_error("experts_gate_up_by_expert: bad argument"); return KTB200_EINVAL; }
+    if (n_tokens <= 0) return KTB200_OK;
+    const int P = n_tokens * top;
+    if (by_expert_staged(staged, P, n_experts) == 4) {
+        constexpr int NT = 4;
+        BY_EXPERT_LAUNCH(experts_gate_up_by_expert_kernel, ff, 2, (size_t)width, (const T*)x, ids, top, P, (const T*)w_gate, (const T*)w_up, (T*)act, width, ff);
+    } else {
+        constexpr int NT = 2;
+        BY_EXPERT_LAUNCH(experts_gate_up_by_expert_kernel, ff, 2, (size_t)width, (const T*)x, ids, top, P, (const T*)w_gate, (const T*)w_up, (T*)act, width, ff);
+    }
+    KTB_LAUNCH_CHECK();
+    return KTB200_OK;
+}
+
+extern "C" int ktb200_experts_down_by_expert(const void* act, const int64_t* ids, const float* weights, int top, int n_experts, const void* w_down, float* pair_rows, float* out,
+                                             int n_tokens, int width, int ff, int staged, int dtype, void* stream) {
+    if (!act || !ids || !weights || !w_down || !pair_rows || !out || top <= 0 || n_experts <= 0 || width <= 0 || ff <= 0) {
+        set_error("experts_down_by_expert: bad argument");
+        return KTB200_EINVAL;
+    }
+    if (n_tokens <= 0) return KTB200_OK;
+    const int P = n_tokens * top;
+    if (by_expert_staged(staged, P, n_experts) == 4) {
+        constexpr int NT = 4;
+        BY_EXPERT_LAUNCH(experts_down_by_expert_kernel, width, 4, (size_t)ff, (const T*)act, ids, P, (const T*)w_down, pair_rows, width, ff);
+    } else {
+        constexpr int NT = 2;
+        BY_EXPERT_LAUNCH(experts_down_by_expert_kernel, width, 4, (size_t)ff, (const T*)act, ids, P, (const T*)w_down, pair_rows, width, ff);
+    }
+    KTB_LAUNCH_CHECK();
+    const long n = (long)n_tokens * width;
+    const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+    experts_combine_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(pair_rows, weights, top, out, n, width);
     KTB_LAUNCH_CHECK();
     return KTB200_OK;
 }

@@ -71,16 +71,13 @@ class LekapelForCausalLM(nn.Module):
         c = self.config
         return PagedStateCache(c.cache_row_widths(), c.width, max_tokens, max_slots, self.device, dtype=self.dtype, page_size=page_size, window=c.max_window())
 
-    def decode_is_capturable(self) -> bool:
-        """Whether a decode step makes no host read (then the engine may replay it as a CUDA graph): the per-pair expert kernels
-        never do; experts whose rows are too long for them do unless the library's grouped GEMM applies (bf16, sizes % 8)."""
+    def decode_is_capturable(self, max_batch: int = 47) -> bool:
+        """Whether a decode step of up to `max_batch` sequences makes no host read (then the engine may replay it as a CUDA
+        graph): the experts' small-batch kernels never do; experts whose rows are too long for them do, unless the library's
+        grouped GEMM applies."""
         for layer in self.layers:
             e = getattr(layer.mlp, "experts", None)
-            if e is None:
-                continue
-            top = layer.mlp.router.top
-            fits = 4 * top * e.ff <= 200 * 1024 and 4 * e.width <= 200 * 1024
-            if not fits and not (self.dtype == torch.bfloat16 and e.width % 8 == 0 and e.ff % 8 == 0 and hasattr(F, "grouped_mm")):
+            if e is not None and not e.small_batches_stay_on_device(layer.mlp.router.top, self.dtype, max_batch):
                 return False
         return True
 

@@ -118,6 +118,8 @@ SEQ_SYMBOLS = {
     "ktb200_poly_norm": (_I, [_VP, _VP, _VP, _F, _I, _I, _I, _VP]),
     "ktb200_experts_gate_up": (_I, [_VP, _VP, _I, _VP, _VP, _VP, _I, _I, _I, _I, _VP]),
     "ktb200_experts_down": (_I, [_VP, _VP, _VP, _I, _VP, _VP, _I, _I, _I, _I, _VP]),
+    "ktb200_experts_gate_up_by_expert": (_I, [_VP, _VP, _I, _I, _VP, _VP, _VP, _I, _I, _I, _I, _I, _VP]),
+    "ktb200_experts_down_by_expert": (_I, [_VP, _VP, _VP, _I, _I, _VP, _VP, _VP, _I, _I, _I, _I, _I, _VP]),
 }
 SEQ_LIB_PATH = os.path.join(_HERE, "libktb200_seq.so")
 _seq_lib = None

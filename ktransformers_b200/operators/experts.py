@@ -528,6 +528,8 @@ class KExpertsDense(nn.Module):
     """Un-quantised (bf16 / fp32) gated-SiLU experts, stacked `[E, ff, width]` / `[E, width, ff]` in HBM, run by the per-pair
     kernels `ktb200_experts_gate_up` / `ktb200_experts_down` (csrc/seq_ops.cu): every (token, slot) pair is a GEMV pair over its
     expert's rows, silu(gate) * up in fp32 with one rounding, the weighted sum over a token's slots in fp32 in slot order.
+    Batches of a few tokens (decode steps of several sequences) take the `_by_expert` kernels: one CTA column per expert
+    finds the pairs routed to it and streams each weight row once for two or four of them, with the same per-pair sums.
     From `grouped_min_tokens` tokens on (the threshold of the quantised experts' grouped path) the pairs are sorted by expert
     and each matrix runs as ONE library grouped GEMM over the per-expert token segments (bf16; fp32 and odd sizes: one GEMM
     per expert), so an expert's weights are read once per step instead of once per pair; the weighted sum over a token's
@@ -536,6 +538,9 @@ class KExpertsDense(nn.Module):
     loops over experts in torch)."""
 
     grouped_min_tokens = 48
+    by_expert_min_tokens = 1        # from here up to the grouped path: kernels that stream an expert's rows once for several pairs
+    by_expert_rows = 4              # most pairs whose rows such a kernel keeps in shared memory at a time
+    by_expert_staged = 0            # 2 or 4 to fix that number; 0: the library chooses from the batch
 
     def __init__(self, width: int, ff: int, experts: int, dtype=torch.bfloat16, device="cuda"):
         super().__init__()
@@ -549,15 +554,48 @@ class KExpertsDense(nn.Module):
             for p, n in zip((self.gate, self.up, self.down), names):
                 p.data[e].copy_(loader.load_tensor(f"{prefix}e{e}.{n}", "cpu"))
 
+    def grouped_is_device_only(self, dtype) -> bool:
+        """whether the grouped path runs as the library's grouped GEMM, which takes the segment ends on the device (no host read)"""
+        return dtype == torch.bfloat16 and self.width % 8 == 0 and self.ff % 8 == 0 and hasattr(nn.functional, "grouped_mm")
+
+    def small_batches_stay_on_device(self, top: int, dtype, max_tokens: int) -> bool:
+        """whether no batch of up to `max_tokens` tokens takes a path that reads the routing on the host"""
+        elem = torch.empty((), dtype=dtype).element_size()
+        per_pair = 4 * top * self.ff <= 200 * 1024 and 4 * self.width <= 200 * 1024
+        by_expert = 4 * (max_tokens * top + 4) + self.by_expert_rows * elem * max(self.width, self.ff) <= 200 * 1024
+        return self.grouped_is_device_only(dtype) or per_pair or by_expert
+
+    def prefers_grouped(self, T: int, top: int, dtype) -> bool:
+        """Below `grouped_min_tokens`: the by-expert kernels stream an expert's rows once per four of its pairs, about
+        `pairs / (4 experts) + 1/2` passes over all experts' weights at ~5 TB/s; the grouped GEMM path reads them once but
+        costs ~0.3 ms of sorting and small launches.  Taken only when it needs no host read, so that a decode step's
+        launches do not depend on the batch size in a way that graph replay could not follow."""
+        if T >= self.grouped_min_tokens:
+            return True
+        if not self.grouped_is_device_only(dtype):
+            return False
+        all_bytes = 3.0 * self.experts * self.ff * self.width * 2
+        passes = T * top / (4.0 * self.experts) + 0.5
+        return (passes - 1.0) * all_bytes / 5e12 > 300e-6
+
     def forward(self, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
         """x [T, width], ids [T, top] int64, weights [T, top] fp32 -> [T, width] fp32"""
         T, top = ids.shape
         fits = 4 * top * self.ff <= 200 * 1024 and 4 * self.width <= 200 * 1024      # the per-pair kernels stage these rows in shared memory
-        if T >= self.grouped_min_tokens or not fits:
+        staged = 4 * (T * top + 4) + self.by_expert_rows * x.element_size() * max(self.width, self.ff)
+        by_expert = T >= self.by_expert_min_tokens and staged <= 200 * 1024
+        if self.prefers_grouped(T, top, x.dtype) or not (fits or by_expert):
             return self.forward_grouped(x, ids, weights)
         act = torch.empty((T * top, self.ff), dtype=x.dtype, device=x.device)
         out = torch.empty((T, self.width), dtype=torch.float32, device=x.device)
         lib, dt, st = native.seq_lib(), TORCH_TO_GGML_HIDDEN[x.dtype], _stream(x.device)
+        if by_expert:
+            pair_rows = torch.empty((T * top, self.width), dtype=torch.float32, device=x.device)
+            native.check_seq(lib.ktb200_experts_gate_up_by_expert(x.data_ptr(), ids.data_ptr(), top, self.experts, self.gate.data_ptr(), self.up.data_ptr(),
+                                                                  act.data_ptr(), T, self.width, self.ff, self.by_expert_staged, dt, st))
+            native.check_seq(lib.ktb200_experts_down_by_expert(act.data_ptr(), ids.data_ptr(), weights.data_ptr(), top, self.experts, self.down.data_ptr(),
+                                                               pair_rows.data_ptr(), out.data_ptr(), T, self.width, self.ff, self.by_expert_staged, dt, st))
+            return out
         native.check_seq(lib.ktb200_experts_gate_up(x.data_ptr(), ids.data_ptr(), top, self.gate.data_ptr(), self.up.data_ptr(), act.data_ptr(), T, self.width,
                                                     self.ff, dt, st))
         native.check_seq(lib.ktb200_experts_down(act.data_ptr(), ids.data_ptr(), weights.data_ptr(), top, self.down.data_ptr(), out.data_ptr(), T, self.width,

@@ -71,7 +71,7 @@ class Engine:
         self.model = model
         self.cache = model.make_cache(max_tokens, max_slots=max_slots, page_size=page_size)
         self.scheduler = Scheduler(self.cache, max_step_tokens=max_step_tokens)
-        self.cuda_graphs = cuda_graphs and self.cache.device.type == "cuda" and getattr(model, "decode_is_capturable", lambda: True)()
+        self.cuda_graphs = cuda_graphs and self.cache.device.type == "cuda" and getattr(model, "decode_is_capturable", lambda n: True)(self.graph_max_batch)
         self._captured, self._seen = {}, {}
 
     @torch.no_grad()

@@ -192,7 +192,7 @@ def kernel_leg(flush, peak_gbs, have_main_lib):
     for name, f, it in (("mla_decode_tc_kernel<split P> (+merge with sink)", f_tc, 5), ("latent_window_attn_kernel", f_cc, 2)):
         ms = timed(f, flush, iters=it, warmup=1)
         rows.append({"kernel": name, "case": f"prompt portion T={T} positions {ctx - T}..{ctx - 1} heads={NH}", "us": ms * 1e3, "TFLOPs": flops / ms / 1e9})
-    # ---- dense experts per pair (decode) : bytes = pairs * 3 * ff * width * 2
+    # ---- dense experts per pair (the fallback for rows too long for the by-expert kernels) : bytes = pairs * 3 * ff * width * 2
     E, top, ff = 32, 8, 2048
     Wg, Wu, Wd = rn(E, ff, D), rn(E, ff, D), rn(E, D, ff)
     for T in (1, 8):
@@ -206,6 +206,19 @@ def kernel_leg(flush, peak_gbs, have_main_lib):
         row("experts_gate_up_kernel", f"T={T} top={top} width={D} ff={ff} bf16", timed(f1, flush), uniq * 2 * ff * D * 2,
             {"kernel": "moe_block_kernel (Q4_K/Q6_K, whole block)", "frac_of_measured_hbm": 0.55, "note": "committed measurement of the DeepSeek path, one token"})
         row("experts_down_kernel", f"T={T} top={top} width={D} ff={ff} bf16", timed(f2, flush), uniq * ff * D * 2)
+    # ---- the same by expert (what decode steps run): an expert's rows cross HBM once per two or four pairs routed to it
+    for T in (1, 8, 16):
+        x = rn(T, D)
+        ids = torch.stack([torch.randperm(E, generator=g, device=dev)[:top] for _ in range(T)]).to(torch.int64)
+        wts = torch.rand(T, top, generator=g, device=dev)
+        act, out, pair_rows = torch.empty(T * top, ff, dtype=bf, device=dev), torch.empty(T, D, device=dev), torch.empty(T * top, D, device=dev)
+        f1 = lambda: native.check_seq(seq.ktb200_experts_gate_up_by_expert(x.data_ptr(), ids.data_ptr(), top, E, Wg.data_ptr(), Wu.data_ptr(), act.data_ptr(), T, D, ff, 0, 30, S()))
+        f2 = lambda: native.check_seq(seq.ktb200_experts_down_by_expert(act.data_ptr(), ids.data_ptr(), wts.data_ptr(), top, E, Wd.data_ptr(), pair_rows.data_ptr(), out.data_ptr(),
+                                                                        T, D, ff, 0, 30, S()))
+        uniq = len(set(ids.flatten().tolist()))
+        row("experts_gate_up_by_expert_kernel", f"T={T} top={top} width={D} ff={ff} bf16", timed(f1, flush), uniq * 2 * ff * D * 2,
+            {"kernel": "moe_block_kernel (Q4_K/Q6_K, whole block)", "frac_of_measured_hbm": 0.55, "note": "committed measurement of the DeepSeek path, one token"})
+        row("experts_down_by_expert_kernel (+combine)", f"T={T} top={top} width={D} ff={ff} bf16", timed(f2, flush), uniq * ff * D * 2)
     return rows
 
 

@@ -209,7 +209,7 @@ def test_poly_norm_mlp(dtype, tol):
 @gpu
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 3e-2)])
 @pytest.mark.parametrize("experts,top,ff,width", [(5, 2, 12, 24), (3, 1, 7, 20), (16, 4, 64, 128), (4, 2, 6, 18)])
-@pytest.mark.parametrize("tokens", [11, 70])                 # per-pair kernels / pairs grouped by expert
+@pytest.mark.parametrize("tokens", [1, 11, 70])              # per-pair kernels / an expert's rows once for several pairs / grouped GEMMs
 def test_softmax_topk_moe(dtype, tol, experts, top, ff, width, tokens):
     from ktransformers_b200.operators.experts import KSoftmaxTopKMoE
     g = torch.Generator().manual_seed(3)
@@ -225,6 +225,30 @@ def test_softmax_topk_moe(dtype, tol, experts, top, ff, width, tokens):
     assert torch.equal(ids.cpu().sort(-1).values, oi.sort(-1).values)
     assert rel(w.cpu().sort(-1).values, ow.sort(-1).values) < 1e-5       # the chosen scores themselves: not re-scaled to sum 1
     assert rel(op(h.cuda()), O.moe_mlp(h.double(), Wd, experts, top)) < tol
+
+
+@gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("experts,top,ff,width,tokens", [(4, 2, 16, 24, 13), (3, 3, 7, 20, 5), (16, 4, 64, 128, 40), (2, 1, 33, 9, 9), (32, 8, 40, 64, 2)])
+def test_experts_by_expert_kernels_equal_the_per_pair_kernels(dtype, experts, top, ff, width, tokens):
+    """many pairs on one expert (more than the kernel stages at once), experts without pairs, 16-byte and element-wise rows: the
+    same activations bit for bit, and the same weighted sums up to the order of the lane sums"""
+    from ktransformers_b200.operators.experts import KExpertsDense
+    g = torch.Generator().manual_seed(11)
+    op = KExpertsDense(width, ff, experts, dtype=dtype)
+    for p in (op.gate, op.up, op.down):
+        p.data.copy_((torch.randn(p.shape, generator=g) * 0.3).to(dtype))
+    x = torch.randn(tokens, width, generator=g).to(dtype).cuda()
+    ids = torch.stack([torch.randperm(experts, generator=g)[:top] for _ in range(tokens)])
+    ids[: tokens // 2] = ids[0]                      # half of the tokens share their experts
+    ids, w = ids.cuda(), torch.rand(tokens, top, generator=g).cuda()
+    by_expert = op(x, ids, w)
+    op.by_expert_min_tokens = 10 ** 9
+    per_pair = op(x, ids, w)
+    assert rel(by_expert, per_pair) < 2e-6
+    want = sum(w[:, j:j + 1].double() * torch.stack([(torch.nn.functional.silu(op.gate[e].double() @ x[t].double()) * (op.up[e].double() @ x[t].double())).to(dtype).double()
+                                                   @ op.down[e].double().T for t, e in enumerate(ids[:, j].tolist())]) for j in range(top))
+    assert rel(by_expert, want) < (1e-5 if dtype == torch.float32 else 2e-2)
 
 
 def attention_alone(spec, dtype, n, page_size, portions, hs_scale_at=None, seed=4, width=24, hs_scale=12.0, tensor_path=True):
@@ -395,9 +419,9 @@ def test_captured_decode_steps_with_a_key_range_cut_for_a_large_cache(tmp_path):
 
 @gpu
 def test_long_expert_rows_decode_without_capture(tmp_path):
-    """top x ff floats beyond the per-pair kernels' shared memory: decode takes the grouped path, which reads the routing counts
+    """expert rows beyond the small-batch kernels' shared memory: decode takes the grouped path, which reads the routing counts
     on the host in fp32, so the engine does not replay such a model's decode steps as graphs; the results still agree"""
-    cfg = U.config([(U.mixer(), U.moe(ff=6600, experts=9, top=8))], width=16, groups=2)
+    cfg = U.config([(U.mixer(), U.moe(ff=13000, experts=5, top=5))], width=16, groups=2)
     eng, om = serve(tmp_path, cfg, "float32", max_tokens=64, max_slots=2)
     assert not eng.model.decode_is_capturable() and not eng.cuda_graphs
     t = toks(14, seed=5)
