@@ -31,7 +31,7 @@ def make_config(s):
     layers = [{"type": "latent_attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": s["dense_ff"]}}]
     layers += [{"type": "latent_attention", "mixer": mixer, "mlp": {"kind": "moe", "expert": {"ff": s["ff"]}, "router": {"experts": s["experts"], "top": s["top"]}}}
                for _ in range(s["n_layers"] - 1)]
-    return {"architecture": "Lekapel", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-5, "groups": 2}, "residual_mult": 0.7, "logit_scale": 0.5, "layers": layers}
+    return {"architecture": "Lekapel", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-5, "groups": 4}, "residual_mult": 0.6, "logit_scale": 1.0, "layers": layers}
 
 
 def random_model(cfg_dict, dtype=torch.bfloat16, device="cuda"):
@@ -129,7 +129,7 @@ def kernel_leg(flush, peak_gbs, have_main_lib):
         xo, h, hs = torch.empty_like(x), torch.empty(T, D, dtype=bf, device=dev), torch.empty(T, D, dtype=bf, device=dev)
         meta = torch.tensor([[-1] + list(range(T - 1)), [-1] * T, [-1] * (T - 1) + [0]], dtype=torch.int32, device=dev)
         st = torch.zeros(2, D, device=dev)
-        fn = lambda: native.check_seq(seq.ktb200_group_rmsnorm_shift(x.data_ptr(), a.data_ptr(), 30, b.data_ptr(), 30, 0.7, xo.data_ptr(), w.data_ptr(), 2, 1e-5, mu.data_ptr(),
+        fn = lambda: native.check_seq(seq.ktb200_group_rmsnorm_shift(x.data_ptr(), a.data_ptr(), 30, b.data_ptr(), 30, 0.6, xo.data_ptr(), w.data_ptr(), 4, 1e-5, mu.data_ptr(),
                                                                      meta[0].data_ptr(), meta[1].data_ptr(), meta[2].data_ptr(), st.data_ptr(), h.data_ptr(), hs.data_ptr(), T, D, 30, S()))
         ours = timed(fn, flush)
         peer = None

@@ -179,14 +179,14 @@ def test_group_norm_and_shift_kernel(dtype, tol, groups, width):
     op.load(DictLoader({"n": w, "s": mu}), "n", "s")
     cache = PagedStateCache([4], width, 64, 2, "cuda", dtype=dtype, page_size=4)
     a_d, b_d = a.to(dtype).cuda(), b.cuda()                      # one branch in the compute dtype, one in fp32
-    xs = x + 0.7 * (a.to(dtype).float() + b)
+    xs = x + 0.6 * (a.to(dtype).float() + b)
     h = O.grouped_rms_norm(xs.double(), w.double(), groups, 1e-5)
     hs, _ = O.token_shift(h, torch.zeros(width, dtype=torch.float64), mu.double())
     # rows 0..3 in one launch, 4 alone, 5..6 together: the shifted rows must not depend on the cut
     outs = []
     for lo, hi in ((0, 4), (4, 5), (5, 7)):
         batch = cache.build_batch([("s", [0] * (hi - lo), [])])
-        xo, ho, so = op(x[lo:hi].cuda().contiguous(), a_d[lo:hi].contiguous(), b_d[lo:hi].contiguous(), 0.7, batch, cache.state[0])
+        xo, ho, so = op(x[lo:hi].cuda().contiguous(), a_d[lo:hi].contiguous(), b_d[lo:hi].contiguous(), 0.6, batch, cache.state[0])
         cache.commit()
         outs.append((xo, ho, so))
     assert rel(torch.cat([o[0] for o in outs]), xs) < 1e-6
@@ -393,7 +393,7 @@ def test_drawn_configurations(tmp_path, seed):
         rot_dim = r.choice([2, 6, 8, 16, 32])
         m = U.mixer(heads=r.choice([1, 2, 5, 8, 12, 20]), dim=r.choice([4, 7, 24, 64]), rot_dim=rot_dim, vdim=r.choice([5, 8, 48]),
                     kv_rank=r.choice([8, 33, 130, 256]), q_rank=r.choice([8, 12, 80]), window=r.choice([1, 2, 9, 31, 32, 33, 64, 65, None]),
-                    base=r.choice([100.0, 1e6]), rot_dims=r.choice([rot_dim, max(2, rot_dim // 4 * 2)]), scale=r.choice([None, 0.125]))
+                    base=r.choice([100.0, 5e5]), rot_dims=r.choice([rot_dim, max(2, rot_dim // 4 * 2)]), scale=r.choice([None, 0.125]))
         e = r.choice([2, 3, 17, 32])
         layers.append((m, r.choice([None, U.dense(ff=r.choice([8, 100, 1030])), U.moe(ff=r.choice([4, 12, 96]), experts=e, top=r.randint(1, min(e, 8)))])))
     cfg = U.config(layers, vocab=r.choice([31, 77, 1000]), width=width, groups=r.choice([1, 2, 4, 8]), eps=r.choice([1e-5, 1e-3]),
