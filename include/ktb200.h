@@ -199,7 +199,7 @@ typedef struct ktb200_gate_config {
     int top_k;
     int n_group;               /* 1 = no grouping */
     int topk_group;
-    int scoring;               /* 0 sigmoid (V3), 1 softmax (V2) */
+    int scoring;               /* 0 sigmoid (V3), 1 softmax (V2), 2 softmax over the chosen logits only, `bias` added to the logits */
     int topk_method;           /* 0 noaux_tc (V3), 1 greedy, 2 group_limited_greedy (V2) */
     int norm_topk_prob;
     float routed_scaling_factor;

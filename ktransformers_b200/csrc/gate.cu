@@ -95,7 +95,7 @@ extern "C" int ktb200_moe_gate_forward(const ktb200_gate_config* c, int qlen, co
         set_error("gate: bad grouping (n_group=%d topk_group=%d)", c->n_group, c->topk_group);
         return KTB200_EINVAL;
     }
-    if (c->scoring < 0 || c->scoring > 1 || c->topk_method < 0 || c->topk_method > 2) { set_error("gate: bad scoring/topk_method"); return KTB200_EINVAL; }
+    if (c->scoring < 0 || c->scoring > 2 || c->topk_method < 0 || c->topk_method > 2) { set_error("gate: bad scoring/topk_method"); return KTB200_EINVAL; }
     if (!is_hidden_type(c->hidden_type) || !c->weight) { set_error("gate: bad hidden_type or null weight"); return KTB200_EINVAL; }
     int dev = 0;
     KTB_CUDA_CHECK(cudaGetDevice(&dev));

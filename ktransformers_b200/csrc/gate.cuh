@@ -107,6 +107,13 @@ __device__ void gate_select_token(const GateParams& pin, int t, float* sm, int64
             if (e < E) logits_out[(long)t * E + e] = v[i];
         }
     }
+    if (p.scoring == 2 && p.bias) {  // the bias belongs to the logits: soft-max over the chosen ones only (top-k, then soft-max)
+#pragma unroll
+        for (int i = 0; i < kGateEPT; i++) {
+            const int e = tid + kGateThreads * i;
+            if (e < E) v[i] += __ldg(p.bias + e);
+        }
+    }
     if (p.scoring == 0) {  // sigmoid
 #pragma unroll
         for (int i = 0; i < kGateEPT; i++) v[i] = __fdiv_rn(1.0f, 1.0f + expf(-v[i]));
@@ -214,7 +221,7 @@ __device__ void gate_select_token(const GateParams& pin, int t, float* sm, int64
         // V2 (modeling_deepseek.py:455-459): normalise XOR scale.
         if (lane < p.top_k) {
             float w = myw;
-            const bool do_norm = p.top_k > 1 && p.norm_topk_prob;
+            const bool do_norm = (p.top_k > 1 && p.norm_topk_prob) || p.scoring == 2;    // soft-max over one chosen logit is 1
             if (do_norm) w = __fdiv_rn(w, wsum + 1e-20f);
             if (p.topk_method == 0 || !do_norm) w = w * p.routed_scaling_factor;
             idx_out[lane] = myidx;

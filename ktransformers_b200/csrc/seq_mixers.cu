@@ -1,0 +1,426 @@
+// Token-major operators of decoder layers with norms on both sides of every sublayer, sigmoid (un-normalised) attention with
+// a distance bias, and gated linear attention with a recurrent state (libktb200_seq.so).
+//
+//   ktb200_group_rmsnorm_sandwich  x_out = x_in + gnorm(y) * w_post + row   then   h = gnorm(x_out) * w_pre
+//                                  (gnorm: RMS norm in `groups` equal consecutive parts; every term optional)
+//   ktb200_qk_norm_cache_write     per-head RMS norm of queries and keys, query temperature by position, paged write of [k | v]
+//   ktb200_sigmoid_bias_attn       o_i = sum_{j <= i} sigmoid(scale q_i.k_j + bias[min(i - j, n - 1)][h] + pb[h]) v_j over the paged
+//                                  cache, grouped query heads, times sigmoid(gate[i][h]); key range cut into splits for few tokens
+//   ktb200_gla_scan                S_t = diag(a_t) S_{t-1} + k_t v_t^T, o_t = S_t^T q_t per sequence portion, state rows in fp32,
+//                                  a_t = sigmoid(z_t + b)^(1/tau)
+//   ktb200_gla_out                 per-head RMS norm of o times silu(gate)
+//   ktb200_xielu                   z > 0: sp(p) z^2 + z/2 ;  z <= 0: (1/2 + sp(q)) (exp(z) - 1 - z) + z/2 ,  sp = softplus
+//
+// Storage type T (bf16 or float) for activations, weights and cache rows; every sum, norm, score, weight, decay and state is
+// fp32.  Rows are addressed through per-token / per-sequence index arrays: one launch serves a ragged batch.
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+#include "seq_common.cuh"
+
+namespace ktb {
+
+__device__ __forceinline__ float sigmoid_f(float x) { return __fdiv_rn(1.0f, 1.0f + expf(-x)); }
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+// log(sigmoid(x)) without overflow on either side
+__device__ __forceinline__ float log_sigmoid_f(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
+
+// ------------------------------------------------------------------------------------------------ sandwich norm
+// One CTA per token.  Shared memory: red[32] | row[D] (the new residual row, when it fits).
+template <typename T>
+__global__ void __launch_bounds__(256) sandwich_norm_kernel(const float* __restrict__ x_in, const void* __restrict__ y, int y_type, const T* __restrict__ w_post,
+                                                            const float* __restrict__ row_add, float* __restrict__ x_out, const T* __restrict__ w_pre,
+                                                            T* __restrict__ h_out, int groups, float eps, int D, int stash) {
+    extern __shared__ __align__(16) float sm[];
+    float* red = sm;
+    float* row = sm + 32;
+    const long t = blockIdx.x;
+    const int tid = threadIdx.x, gs = D / groups;
+    const bool vec = (gs & 3) == 0;
+    for (int g = 0; g < groups; g++) {
+        const int lo = g * gs;
+        float inv = 1.f;
+        if (w_post) {
+            float s = 0.f;
+            if (vec) {
+                for (int i = tid * 4; i < gs; i += blockDim.x * 4) {
+                    const float4 v = load4_hidden(y, t * D + lo + i, y_type);
+                    s += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+                }
+            } else {
+                for (int i = tid; i < gs; i += blockDim.x) { const float v = load_hidden(y, t * D + lo + i, y_type); s += v * v; }
+            }
+            s = block_sum(s, red);
+            inv = 1.0f / sqrtf(s / (float)gs + eps);
+        }
+        float s2 = 0.f;
+        for (int i = tid; i < gs; i += blockDim.x) {
+            const long at = t * D + lo + i;
+            float v = load_hidden(y, at, y_type);
+            if (w_post) v = v * inv * to_f(w_post[lo + i]);
+            if (x_in) v = x_in[at] + v;
+            if (row_add) v += row_add[lo + i];
+            if (x_out) x_out[at] = v;
+            if (stash) row[lo + i] = v;
+            s2 += v * v;
+        }
+        if (w_pre) {
+            s2 = block_sum(s2, red);
+            const float inv2 = 1.0f / sqrtf(s2 / (float)gs + eps);
+            for (int i = tid; i < gs; i += blockDim.x) {      // the same thread wrote these values
+                const float v = stash ? row[lo + i] : x_out[t * D + lo + i];
+                h_out[t * D + lo + i] = from_f<T>(v * inv2 * to_f(w_pre[lo + i]));
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ attention: norms, temperature, cache write
+// One CTA per token, a warp per head.  proj row: [q H*d | k G*d | v G*dv | ...].  Cache row: [k G*d | v G*dv].
+template <typename T>
+__global__ void __launch_bounds__(256) qk_norm_cache_write_kernel(const T* __restrict__ proj, long proj_stride, int H, int G, int d, int dv, const T* __restrict__ qw,
+                                                                  const T* __restrict__ kw, float eps, float temp_coef, int temp_every, const int* __restrict__ pos,
+                                                                  const int* __restrict__ slot, const int* __restrict__ page_table, int max_pages, int page_size,
+                                                                  T* __restrict__ cache, T* __restrict__ q_out) {
+    const long t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int p = pos[t];
+    const float temp = 1.0f + temp_coef * logf((float)((p + 1) / temp_every) + 1.0f);
+    const T* row = proj + t * proj_stride;
+    const long crow = ((long)page_table[(long)slot[t] * max_pages + (p / page_size) % max_pages] * page_size + p % page_size) * ((long)G * (d + dv));
+    for (int hh = warp; hh < H + G; hh += nw) {
+        const bool is_q = hh < H;
+        const T* src = row + (long)hh * d;
+        float s = 0.f;
+        for (int i = lane; i < d; i += 32) { const float v = to_f(src[i]); s += v * v; }
+        s = warp_sum(s);
+        const float inv = 1.0f / sqrtf(s / (float)d + eps);
+        if (is_q) {
+            for (int i = lane; i < d; i += 32) q_out[(t * H + hh) * d + i] = from_f<T>(to_f(src[i]) * inv * to_f(qw[i]) * temp);
+        } else {
+            for (int i = lane; i < d; i += 32) cache[crow + (long)(hh - H) * d + i] = from_f<T>(to_f(src[i]) * inv * to_f(kw[i]));
+        }
+    }
+    const T* v = row + (long)(H + G) * d;
+    for (int i = threadIdx.x; i < G * dv; i += blockDim.x) cache[crow + (long)G * d + i] = v[i];
+}
+
+// ------------------------------------------------------------------------------------------------ sigmoid attention, CUDA cores
+// grid (tokens, G * head blocks, splits); a warp per query head (HB = blockDim / 32 heads of ONE key/value head per CTA).  Tiles of
+// 32 keys in shared memory as fp32: lane = key for the scores, lane = value column for the weighted sum.  Shared memory:
+//   q [HB][d] | K [32][d + 1] | V [32][dv] | bias [HB][n_bias]
+constexpr int kAttnTile = 32;
+constexpr int kAttnMaxCols = 8;      // value columns per lane: vdim <= 256
+template <typename T>
+__global__ void __launch_bounds__(256) sigmoid_attn_kernel(const T* __restrict__ q, int H, int G, int d, int dv, float scale, const float* __restrict__ bias, int n_bias,
+                                                           const float* __restrict__ pb, const int* __restrict__ pos, const int* __restrict__ slot,
+                                                           const int* __restrict__ page_table, int max_pages, int page_size, const T* __restrict__ cache,
+                                                           const T* __restrict__ gate, long gate_stride, T* __restrict__ out, float* __restrict__ partial, int n_tokens) {
+    extern __shared__ __align__(16) float sm[];
+    const int HB = blockDim.x >> 5, R = H / G, hblocks = (R + HB - 1) / HB;
+    const int g = blockIdx.y / hblocks, hb = blockIdx.y % hblocks;
+    const long t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int r = hb * HB + warp, h = g * R + r;
+    const bool live = r < R;
+    float* qs = sm;
+    float* Ks = qs + HB * d;
+    float* Vs = Ks + kAttnTile * (d + 1);
+    float* bs = Vs + kAttnTile * dv;
+    const int p = pos[t];
+    // key range of this split
+    const int splits = gridDim.z, n_keys = p + 1;
+    const int per = ((n_keys + splits - 1) / splits + kAttnTile - 1) / kAttnTile * kAttnTile;
+    const int k_lo = blockIdx.z * per, k_hi = min(n_keys, k_lo + per);
+    float acc[kAttnMaxCols];
+#pragma unroll
+    for (int c = 0; c < kAttnMaxCols; c++) acc[c] = 0.f;
+    if (k_lo < k_hi) {
+        if (live) {
+            for (int i = lane; i < d; i += 32) qs[warp * d + i] = to_f(q[(t * H + h) * d + i]) * scale;
+            for (int i = lane; i < n_bias; i += 32) bs[warp * n_bias + i] = bias[(long)i * H + h] + pb[h];
+        }
+        const int* pt = page_table + (long)slot[t] * max_pages;
+        const long cw = (long)G * (d + dv);
+        for (int j0 = k_lo; j0 < k_hi; j0 += kAttnTile) {
+            __syncthreads();
+            const int nk = min(kAttnTile, k_hi - j0);
+            for (int i = threadIdx.x; i < nk * d; i += blockDim.x) {
+                const int j = i / d, c = i - j * d, kp = j0 + j;
+                Ks[j * (d + 1) + c] = to_f(cache[((long)pt[(kp / page_size) % max_pages] * page_size + kp % page_size) * cw + (long)g * d + c]);
+            }
+            for (int i = threadIdx.x; i < nk * dv; i += blockDim.x) {
+                const int j = i / dv, c = i - j * dv, kp = j0 + j;
+                Vs[j * dv + c] = to_f(cache[((long)pt[(kp / page_size) % max_pages] * page_size + kp % page_size) * cw + (long)G * d + (long)g * dv + c]);
+            }
+            __syncthreads();
+            if (live) {
+                float w = 0.f;
+                if (lane < nk) {
+                    float s = 0.f;
+                    const float* kr = Ks + lane * (d + 1);
+                    const float* qr = qs + warp * d;
+                    for (int i = 0; i < d; i++) s = fmaf(qr[i], kr[i], s);
+                    const int dist = p - (j0 + lane);
+                    w = sigmoid_f(s + bs[warp * n_bias + min(dist, n_bias - 1)]);
+                }
+                for (int j = 0; j < nk; j++) {
+                    const float wj = __shfl_sync(0xffffffffu, w, j);
+#pragma unroll
+                    for (int c = 0; c < kAttnMaxCols; c++)
+                        if (lane + 32 * c < dv) acc[c] = fmaf(wj, Vs[j * dv + lane + 32 * c], acc[c]);
+                }
+            }
+        }
+    }
+    if (!live) return;
+    if (partial) {
+#pragma unroll
+        for (int c = 0; c < kAttnMaxCols; c++)
+            if (lane + 32 * c < dv) partial[(((long)blockIdx.z * n_tokens + t) * H + h) * dv + lane + 32 * c] = acc[c];
+    } else {
+        const float gt = sigmoid_f(to_f(gate[t * gate_stride + h]));
+#pragma unroll
+        for (int c = 0; c < kAttnMaxCols; c++)
+            if (lane + 32 * c < dv) out[(t * H + h) * dv + lane + 32 * c] = from_f<T>(acc[c] * gt);
+    }
+}
+
+// sum of the splits' partial rows in split order, times the head's gate
+template <typename T>
+__global__ void sigmoid_attn_merge_kernel(const float* __restrict__ partial, int splits, const T* __restrict__ gate, long gate_stride, T* __restrict__ out, long n_tokens, int H, int dv) {
+    const long n = n_tokens * H * dv;
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+        float s = 0.f;
+        for (int k = 0; k < splits; k++) s += partial[k * n + i];
+        const long th = i / dv, t = th / H;
+        const int h = (int)(th - t * H);
+        out[i] = from_f<T>(s * sigmoid_f(to_f(gate[t * gate_stride + h])));
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ gated linear attention
+// grid (sequence portions, heads, column blocks of 32 value columns); 8 warps; thread (warp w, lane) keeps S[i][col] for the
+// key channels i = w + 8 r in registers.  Tokens run in order in chunks of kGlaChunk staged in shared memory; per token every
+// warp leaves its part of o in shared memory, and the parts are summed in warp order once per chunk.  The arithmetic of a token
+// does not depend on where a portion starts or ends.
+constexpr int kGlaChunk = 16;
+constexpr int kGlaWarps = 8;
+constexpr int kGlaRows = 32;         // key channels per thread: dim <= 256
+template <typename T>
+__global__ void __launch_bounds__(256) gla_scan_kernel(const T* __restrict__ proj, long proj_stride, int q_off, int k_off, int v_off, const T* __restrict__ z, long z_stride,
+                                                       const T* __restrict__ z_bias, float inv_tau, float q_scale, int H, int d, int dv, const int* __restrict__ seqs,
+                                                       int seqs_stride, float* __restrict__ state, float* __restrict__ o_out) {
+    extern __shared__ __align__(16) float sm[];
+    float* qs = sm;                             // [chunk][d]
+    float* ks = qs + kGlaChunk * d;             // [chunk][d]
+    float* as = ks + kGlaChunk * d;             // [chunk][d]
+    float* vs = as + kGlaChunk * d;             // [chunk][32]
+    float* part = vs + kGlaChunk * 32;          // [chunk][warps][32]
+    const int s = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * 32;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, col = c0 + lane;
+    const int start = seqs[s], len = seqs[seqs_stride + s], rd = seqs[2 * seqs_stride + s], wr = seqs[3 * seqs_stride + s];
+    const long srow = (long)H * d * dv;
+    float S[kGlaRows];
+#pragma unroll
+    for (int r = 0; r < kGlaRows; r++) {
+        const int i = warp + kGlaWarps * r;
+        S[r] = (rd >= 0 && i < d && col < dv) ? state[rd * srow + ((long)h * d + i) * dv + col] : 0.f;
+    }
+    for (int t0 = 0; t0 < len; t0 += kGlaChunk) {
+        const int nt = min(kGlaChunk, len - t0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < nt * d; i += blockDim.x) {
+            const int tt = i / d, c = i - tt * d;
+            const long row = (long)(start + t0 + tt);
+            qs[i] = to_f(proj[row * proj_stride + q_off + h * d + c]) * q_scale;
+            ks[i] = to_f(proj[row * proj_stride + k_off + h * d + c]);
+            as[i] = expf(log_sigmoid_f(to_f(z[row * z_stride + h * d + c]) + to_f(z_bias[h * d + c])) * inv_tau);
+        }
+        for (int i = threadIdx.x; i < nt * 32; i += blockDim.x) {
+            const int tt = i >> 5, c = c0 + (i & 31);
+            vs[i] = c < dv ? to_f(proj[(long)(start + t0 + tt) * proj_stride + v_off + h * dv + c]) : 0.f;
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; tt++) {
+            const float v = vs[tt * 32 + lane];
+            const float* qr = qs + tt * d;
+            const float* kr = ks + tt * d;
+            const float* ar = as + tt * d;
+            float po = 0.f;
+#pragma unroll
+            for (int r = 0; r < kGlaRows; r++) {
+                const int i = warp + kGlaWarps * r;
+                if (i < d) {
+                    S[r] = fmaf(ar[i], S[r], kr[i] * v);
+                    po = fmaf(S[r], qr[i], po);
+                }
+            }
+            part[(tt * kGlaWarps + warp) * 32 + lane] = po;
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < nt * 32; i += blockDim.x) {
+            const int tt = i >> 5, c = c0 + (i & 31);
+            float o = 0.f;
+#pragma unroll
+            for (int w = 0; w < kGlaWarps; w++) o += part[(tt * kGlaWarps + w) * 32 + (i & 31)];
+            if (c < dv) o_out[((long)(start + t0 + tt) * H + h) * dv + c] = o;
+        }
+    }
+    if (wr >= 0) {
+#pragma unroll
+        for (int r = 0; r < kGlaRows; r++) {
+            const int i = warp + kGlaWarps * r;
+            if (i < d && col < dv) state[wr * srow + ((long)h * d + i) * dv + col] = S[r];
+        }
+    }
+}
+
+// out[t][h][c] = o[t][h][c] / sqrt(mean_c o^2 + eps) * w[c] * silu(gate[t][h][c]); a warp per (token, head)
+template <typename T>
+__global__ void __launch_bounds__(256) gla_out_kernel(const float* __restrict__ o, const T* __restrict__ w, float eps, const T* __restrict__ gate, long gate_stride,
+                                                      T* __restrict__ out, long n_rows, int H, int dv) {
+    const int lane = threadIdx.x & 31;
+    for (long row = blockIdx.x * (long)(blockDim.x >> 5) + (threadIdx.x >> 5); row < n_rows; row += (long)gridDim.x * (blockDim.x >> 5)) {
+        const float* src = o + row * dv;
+        float s = 0.f;
+        for (int c = lane; c < dv; c += 32) s += src[c] * src[c];
+        s = warp_sum(s);
+        const float inv = 1.0f / sqrtf(s / (float)dv + eps);
+        const long t = row / H;
+        const int h = (int)(row - t * H);
+        for (int c = lane; c < dv; c += 32) out[row * dv + c] = from_f<T>(src[c] * inv * to_f(w[c]) * act_silu(to_f(gate[t * gate_stride + (long)h * dv + c])));
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ xIELU
+template <typename T>
+__global__ void xielu_kernel(const T* __restrict__ z, T* __restrict__ out, const float* __restrict__ pq, long n) {
+    const float ap = softplus_f(pq[0]), an = 0.5f + softplus_f(pq[1]);
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+        const float v = to_f(z[i]);
+        out[i] = from_f<T>(v > 0.f ? fmaf(ap * v, v, 0.5f * v) : fmaf(an, expm1f(v) - v, 0.5f * v));
+    }
+}
+
+}  // namespace ktb
+
+using namespace ktb;
+
+#define SEQ_DISPATCH(dtype, ...)                                                           \
+    do {                                                                                   \
+        if ((dtype) == KTB200_TYPE_BF16) { using T = __nv_bfloat16; __VA_ARGS__; }         \
+        else if ((dtype) == KTB200_TYPE_F32) { using T = float; __VA_ARGS__; }             \
+        else { set_error("dtype must be bf16 or f32"); return KTB200_EINVAL; }             \
+    } while (0)
+#define GRANT_SMEM(kernel, smem)                                                                                                       \
+    do {                                                                                                                               \
+        static size_t granted = 48 * 1024;                                                                                             \
+        if ((smem) > granted) { KTB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(smem))); granted = (smem); } \
+    } while (0)
+
+static int grid_for(long n, int per_block) {
+    const long b = (n + per_block - 1) / per_block;
+    return (int)(b < 148 * 8 ? (b < 1 ? 1 : b) : 148 * 8);
+}
+
+extern "C" int ktb200_group_rmsnorm_sandwich(const float* x_in, const void* y, int y_type, const void* w_post, const float* row_add, float* x_out, const void* w_pre,
+                                             void* h_out, int groups, float eps, int n_tokens, int width, int dtype, void* stream) {
+    if (n_tokens <= 0) return KTB200_OK;
+    if (!y || groups <= 0 || width <= 0 || width % groups || (w_pre && !h_out) || (!x_out && !w_pre) || (y_type != KTB200_TYPE_BF16 && y_type != KTB200_TYPE_F32)) {
+        set_error("group_rmsnorm_sandwich: bad argument");
+        return KTB200_EINVAL;
+    }
+    const int stash = (size_t)width * sizeof(float) <= 160 * 1024 || !x_out;
+    if (!stash && !x_out) { set_error("group_rmsnorm_sandwich: row too wide"); return KTB200_EINVAL; }
+    const size_t smem = (32 + (stash ? (size_t)width : 0)) * sizeof(float);
+    SEQ_DISPATCH(dtype, {
+        GRANT_SMEM(sandwich_norm_kernel<T>, smem);
+        sandwich_norm_kernel<T><<<n_tokens, 256, smem, (cudaStream_t)stream>>>(x_in, y, y_type, (const T*)w_post, row_add, x_out, (const T*)w_pre, (T*)h_out, groups, eps, width, stash);
+    });
+    KTB_LAUNCH_CHECK();
+    return KTB200_OK;
+}
+
+extern "C" int ktb200_qk_norm_cache_write(const void* proj, long proj_stride, int heads, int kv_heads, int dim, int vdim, const void* q_norm_w, const void* k_norm_w, float eps,
+                                          float temp_coef, int temp_every, const int* pos, const int* slot, const int* page_table, int max_pages, int page_size, void* cache,
+                                          void* q_out, int n_tokens, int dtype, void* stream) {
+    if (!proj || !q_norm_w || !k_norm_w || !pos || !slot || !page_table || !cache || !q_out || heads <= 0 || kv_heads <= 0 || heads % kv_heads || dim <= 0 || vdim <= 0 ||
+        temp_every <= 0 || page_size <= 0 || max_pages <= 0) {
+        set_error("qk_norm_cache_write: bad argument");
+        return KTB200_EINVAL;
+    }
+    if (n_tokens <= 0) return KTB200_OK;
+    SEQ_DISPATCH(dtype, (qk_norm_cache_write_kernel<T><<<n_tokens, 256, 0, (cudaStream_t)stream>>>((const T*)proj, proj_stride, heads, kv_heads, dim, vdim, (const T*)q_norm_w,
+                                                                                                   (const T*)k_norm_w, eps, temp_coef, temp_every, pos, slot, page_table,
+                                                                                                   max_pages, page_size, (T*)cache, (T*)q_out)));
+    KTB_LAUNCH_CHECK();
+    return KTB200_OK;
+}
+
+extern "C" size_t ktb200_sigmoid_bias_attn_workspace(int n_tokens, int heads, int vdim, int splits) {
+    return splits > 1 ? (size_t)splits * n_tokens * heads * vdim * sizeof(float) : 0;
+}
+
+extern "C" int ktb200_sigmoid_bias_attn(const void* q, int heads, int kv_heads, int dim, int vdim, float scale, const float* bias, int n_bias, const float* head_bias,
+                                        const int* pos, const int* slot, const int* page_table, int max_pages, int page_size, const void* cache, const void* gate,
+                                        long gate_stride, void* out, int n_tokens, int splits, float* workspace, int dtype, void* stream) {
+    if (!q || !bias || !head_bias || !pos || !slot || !page_table || !cache || !gate || !out || heads <= 0 || kv_heads <= 0 || heads % kv_heads || dim <= 0 || vdim <= 0 ||
+        vdim > 32 * kAttnMaxCols || n_bias <= 0 || splits < 1 || (splits > 1 && !workspace)) {
+        set_error("sigmoid_bias_attn: bad argument");
+        return KTB200_EINVAL;
+    }
+    if (n_tokens <= 0) return KTB200_OK;
+    const int R = heads / kv_heads, HB = R < 8 ? R : 8, hblocks = (R + HB - 1) / HB;
+    const size_t smem = ((size_t)HB * dim + (size_t)kAttnTile * (dim + 1) + (size_t)kAttnTile * vdim + (size_t)HB * n_bias) * sizeof(float);
+    if (smem > 200 * 1024) { set_error("sigmoid_bias_attn: head too wide for shared memory"); return KTB200_EINVAL; }
+    SEQ_DISPATCH(dtype, {
+        GRANT_SMEM(sigmoid_attn_kernel<T>, smem);
+        sigmoid_attn_kernel<T><<<dim3(n_tokens, kv_heads * hblocks, splits), HB * 32, smem, (cudaStream_t)stream>>>(
+            (const T*)q, heads, kv_heads, dim, vdim, scale, bias, n_bias, head_bias, pos, slot, page_table, max_pages, page_size, (const T*)cache, (const T*)gate, gate_stride,
+            (T*)out, splits > 1 ? workspace : nullptr, n_tokens);
+        KTB_LAUNCH_CHECK();
+        if (splits > 1) {
+            sigmoid_attn_merge_kernel<T><<<grid_for((long)n_tokens * heads * vdim, 256), 256, 0, (cudaStream_t)stream>>>(workspace, splits, (const T*)gate, gate_stride, (T*)out,
+                                                                                                                       n_tokens, heads, vdim);
+            KTB_LAUNCH_CHECK();
+        }
+    });
+    return KTB200_OK;
+}
+
+extern "C" int ktb200_gla_scan(const void* proj, long proj_stride, int q_off, int k_off, int v_off, const void* z, long z_stride, const void* z_bias, float tau, int heads,
+                               int dim, int vdim, const int* seqs, int seqs_stride, int n_seqs, float* state, float* o_out, int dtype, void* stream) {
+    if (!proj || !z || !z_bias || !seqs || !state || !o_out || heads <= 0 || dim <= 0 || dim > kGlaWarps * kGlaRows || vdim <= 0 || !(tau > 0.f)) {
+        set_error("gla_scan: bad argument (dim <= %d)", kGlaWarps * kGlaRows);
+        return KTB200_EINVAL;
+    }
+    if (n_seqs <= 0) return KTB200_OK;
+    const size_t smem = ((size_t)3 * kGlaChunk * dim + kGlaChunk * 32 + (size_t)kGlaChunk * kGlaWarps * 32) * sizeof(float);
+    SEQ_DISPATCH(dtype, {
+        GRANT_SMEM(gla_scan_kernel<T>, smem);
+        gla_scan_kernel<T><<<dim3(n_seqs, heads, (vdim + 31) / 32), kGlaWarps * 32, smem, (cudaStream_t)stream>>>(
+            (const T*)proj, proj_stride, q_off, k_off, v_off, (const T*)z, z_stride, (const T*)z_bias, 1.0f / tau, 1.0f / sqrtf((float)dim), heads, dim, vdim, seqs, seqs_stride,
+            state, o_out);
+    });
+    KTB_LAUNCH_CHECK();
+    return KTB200_OK;
+}
+
+extern "C" int ktb200_gla_out(const float* o, const void* norm_w, float eps, const void* gate, long gate_stride, void* out, int n_tokens, int heads, int vdim, int dtype,
+                              void* stream) {
+    if (!o || !norm_w || !gate || !out || heads <= 0 || vdim <= 0) { set_error("gla_out: bad argument"); return KTB200_EINVAL; }
+    if (n_tokens <= 0) return KTB200_OK;
+    const long rows = (long)n_tokens * heads;
+    SEQ_DISPATCH(dtype, (gla_out_kernel<T><<<grid_for(rows, 8), 256, 0, (cudaStream_t)stream>>>(o, (const T*)norm_w, eps, (const T*)gate, gate_stride, (T*)out, rows, heads, vdim)));
+    KTB_LAUNCH_CHECK();
+    return KTB200_OK;
+}
+
+extern "C" int ktb200_xielu(const void* z, void* out, const float* pq, long n, int dtype, void* stream) {
+    if (!z || !out || !pq) { set_error("xielu: bad argument"); return KTB200_EINVAL; }
+    if (n <= 0) return KTB200_OK;
+    SEQ_DISPATCH(dtype, (xielu_kernel<T><<<grid_for(n, 256 * 4), 256, 0, (cudaStream_t)stream>>>((const T*)z, (T*)out, pq, n)));
+    KTB_LAUNCH_CHECK();
+    return KTB200_OK;
+}

@@ -279,6 +279,8 @@ __global__ void __launch_bounds__(256) poly_norm_kernel(const T* __restrict__ z,
 }
 
 // ------------------------------------------------------------------------------------------------ dense experts, per pair
+// Two kinds of expert: gated (silu(W_gate x) * W_up x) and, with no gate matrix (Wg == nullptr), relu(W_up x)^2.
+__device__ __forceinline__ float act_relu_sq(float x) { const float r = fmaxf(x, 0.f); return r * r; }
 // grid (pairs, row blocks); a warp owns ff rows r = blockIdx.y * nw + warp (+ stride); the token's row sits in shared memory.
 template <typename T>
 __global__ void __launch_bounds__(256) experts_gate_up_kernel(const T* __restrict__ x, const int64_t* __restrict__ ids, int top, const T* __restrict__ Wg, const T* __restrict__ Wu,
@@ -290,8 +292,16 @@ __global__ void __launch_bounds__(256) experts_gate_up_kernel(const T* __restric
     for (int i = threadIdx.x; i < D; i += blockDim.x) xs[i] = to_f(x[t * D + i]);
     __syncthreads();
     const long e = ids[p];
-    const T* g = Wg + e * (long)F * D;
     const T* u = Wu + e * (long)F * D;
+    if (!Wg) {      // experts without a gate matrix: relu(up)^2
+        const bool vec = rows_vectorise(Wu, D);
+        for (int r = blockIdx.y * nw + warp; r < F; r += gridDim.y * nw) {
+            const float su = warp_sum(lane_dot(u + (long)r * D, xs, D, lane, vec));
+            if (lane == 0) act[p * F + r] = from_f<T>(act_relu_sq(su));
+        }
+        return;
+    }
+    const T* g = Wg + e * (long)F * D;
     const bool vec = rows_vectorise(Wg, D) && rows_vectorise(Wu, D);
     for (int r = blockIdx.y * nw + warp; r < F; r += gridDim.y * nw) {
         float sg = lane_dot(g + (long)r * D, xs, D, lane, vec);
@@ -458,12 +468,34 @@ __global__ void __launch_bounds__(256) experts_gate_up_by_expert_kernel(const T*
     if (n == 0) return;
     const T* g = Wg + (long)e * F * D;
     const T* u = Wu + (long)e * F * D;
-    const bool vec = rows_vectorise(Wg, D) && rows_vectorise(Wu, D) && rows_vectorise(x, D);
+    const bool vec = (!Wg || rows_vectorise(Wg, D)) && rows_vectorise(Wu, D) && rows_vectorise(x, D);
     for (int c = 0; c < n; c += NT) {
         const int m = n - c < NT ? n - c : NT;
         if (c) __syncthreads();      // the rows of the previous pairs are consumed
         stage_rows(xs, x, list + c, top, m, D, vec);
         __syncthreads();
+        if (!Wg) {      // no gate matrix: four up rows at a time, relu(.)^2
+            for (int r = (blockIdx.y * nw + warp) * 4; r < F; r += gridDim.y * nw * 4) {
+                const T* const w[4] = {u + (long)r * D, u + (long)(r + 1 < F ? r + 1 : r) * D, u + (long)(r + 2 < F ? r + 2 : r) * D, u + (long)(r + 3 < F ? r + 3 : r) * D};
+                float s[4][NT];
+#pragma unroll
+                for (int q = 0; q < 4; q++)
+#pragma unroll
+                    for (int k = 0; k < NT; k++) s[q][k] = 0.f;
+                lane_dot_rows<NT, 4>(w, xs, D, m, lane, vec, s);
+#pragma unroll
+                for (int k = 0; k < NT; k++) {
+                    if (k < m) {
+#pragma unroll
+                        for (int q = 0; q < 4; q++) {
+                            const float a = warp_sum(s[q][k]);
+                            if (lane == q && r + q < F) act[(long)list[c + k] * F + r + q] = from_f<T>(act_relu_sq(a));
+                        }
+                    }
+                }
+            }
+            continue;
+        }
         for (int r = (blockIdx.y * nw + warp) * 2; r < F; r += gridDim.y * nw * 2) {
             const int r1 = r + 1 < F ? r + 1 : r;      // an odd last row is done twice and stored once
             const T* const w[4] = {g + (long)r * D, u + (long)r * D, g + (long)r1 * D, u + (long)r1 * D};
@@ -624,7 +656,7 @@ extern "C" int ktb200_poly_norm(const void* z, void* out, const float* coef, flo
 
 extern "C" int ktb200_experts_gate_up(const void* x, const int64_t* ids, int top, const void* w_gate, const void* w_up, void* act, int n_tokens, int width, int ff, int dtype,
                                       void* stream) {
-    if (!x || !ids || !w_gate || !w_up || !act || top <= 0 || width <= 0 || ff <= 0 || width * sizeof(float) > 200 * 1024) { set_error("experts_gate_up: bad argument"); return KTB200_EINVAL; }
+    if (!x || !ids || !w_up || !act || top <= 0 || width <= 0 || ff <= 0 || width * sizeof(float) > 200 * 1024) { set_error("experts_gate_up: bad argument"); return KTB200_EINVAL; }
     if (n_tokens <= 0) return KTB200_OK;
     const size_t smem = (size_t)width * sizeof(float);
     int ry = (ff + 7) / 8;   // row blocks: enough CTAs to fill 148 SMs several times over when there are few pairs
@@ -676,7 +708,7 @@ static int by_expert_staged(int staged, int pairs, int n_experts) { return stage
 
 extern "C" int ktb200_experts_gate_up_by_expert(const void* x, const int64_t* ids, int top, int n_experts, const void* w_gate, const void* w_up, void* act, int n_tokens, int width,
                                                 int ff, int staged, int dtype, void* stream) {
-    if (!x || !ids || !w_gate || !w_up || !act || top <= 0 || n_experts <= 0 || width <= 0 || ff <= 0) { set_error("experts_gate_up_by_expert: bad argument"); return KTB200_EINVAL; }
+    if (!x || !ids || !w_up || !act || top <= 0 || n_experts <= 0 || width <= 0 || ff <= 0) { set_error("experts_gate_up_by_expert: bad argument"); return KTB200_EINVAL; }
     if (n_tokens <= 0) return KTB200_OK;
     const int P = n_tokens * top;
     if (by_expert_staged(staged, P, n_experts) == 4) {

@@ -74,13 +74,17 @@ class ForwardBatch:
 
     `tokens`, `pos`, `slot` [T]; for layers that keep a previous-token row: `prev_idx` (row of the previous token inside this
     step or -1), `rd_row` / `wr_row` (state rows to read when the previous token came in an earlier step / to write for the
-    last token of a sequence's portion; -1: none).  `want` [W]: rows whose logits the caller asked for."""
+    last token of a sequence's portion; -1: none).  `seqs` [4, >= n_seqs]: the same per sequence portion, for layers whose
+    state is a recurrence over the portion's tokens.  `want` [W]: rows whose logits the caller asked for."""
 
-    __slots__ = ("tokens", "pos", "slot", "prev_idx", "rd_row", "wr_row", "want", "n_tokens", "max_kv")
+    __slots__ = ("tokens", "pos", "slot", "prev_idx", "rd_row", "wr_row", "want", "n_tokens", "max_kv", "seqs", "n_seqs")
 
-    def __init__(self, meta: torch.Tensor, tokens: torch.Tensor, want: torch.Tensor, max_kv: int):
+    def __init__(self, meta: torch.Tensor, tokens: torch.Tensor, want: torch.Tensor, max_kv: int, n_seqs: int = 0):
         self.pos, self.slot, self.prev_idx, self.rd_row, self.wr_row = meta[0], meta[1], meta[2], meta[3], meta[4]
         self.tokens, self.want, self.n_tokens, self.max_kv = tokens, want, int(tokens.shape[0]), max_kv
+        # per sequence portion, for layers that carry a recurrent state: rows (first token's row, token count, state row to
+        # read or -1, state row to write) in the first n_seqs columns
+        self.seqs, self.n_seqs = (meta[5:9] if meta.shape[0] >= 9 else None), n_seqs
 
 
 class PagedStateCache:
@@ -101,15 +105,21 @@ class PagedStateCache:
     The reference's StaticCache (archive/ktransformers/models/custom_cache.py:26-200) keeps a static identity page table per
     batch row; this manager adds allocation, release and the recurrent rows."""
 
-    def __init__(self, row_widths, state_width: int, max_tokens: int, max_slots: int, device, dtype=torch.bfloat16, page_size: int = 64,
+    def __init__(self, row_widths, state_width, max_tokens: int, max_slots: int, device, dtype=torch.bfloat16, page_size: int = 64,
                  window: Optional[int] = None):
+        """`row_widths[l]`: cache values per token of cache layer l (0: the layer caches no rows); `state_width`: fp32 state
+        values per sequence, one number for all layers or one per layer (0: none).  A model whose layers run several times
+        with separate caches counts every run as a cache layer."""
         self.device, self.dtype, self.page_size, self.window = torch.device(device), dtype, int(page_size), window
         self.max_slots = int(max_slots)
         # every live sequence may hold one partly filled page at each end of its range
         self.num_pages = (int(max_tokens) + page_size - 1) // page_size + 2 * self.max_slots
         self.max_pages_per_seq = (int(max_tokens) + page_size - 1) // page_size + 2
         self.key_cache = [torch.zeros((self.num_pages, page_size, int(w)), dtype=dtype, device=device) for w in row_widths]
-        self.state = [torch.zeros((2 * self.max_slots, int(state_width)), dtype=torch.float32, device=device) for _ in row_widths]
+        state_widths = [int(state_width)] * len(row_widths) if isinstance(state_width, int) else [int(w) for w in state_width]
+        if len(state_widths) != len(row_widths):
+            raise ValueError("one state width per cache layer")
+        self.state = [torch.zeros((2 * self.max_slots, w), dtype=torch.float32, device=device) for w in state_widths]
         self.page_table = torch.zeros((self.max_slots, self.max_pages_per_seq), dtype=torch.int32, device=device)
         self._table_host = torch.zeros((self.max_slots, self.max_pages_per_seq), dtype=torch.int32)
         self._free_pages = list(range(self.num_pages - 1, -1, -1))
@@ -198,14 +208,16 @@ class PagedStateCache:
 
     def build_batch(self, entries, want_all: bool = False, static=None) -> ForwardBatch:
         """entries: [(seq_id, tokens, want)] — reserve pages, lay out the per-token index rows, one host-to-device copy.
-        `static` = (meta [5, T] int32, tokens [T] int64) device buffers of a captured step: the rows are copied into them and
+        `static` = (meta [9, T] int32, tokens [T] int64) device buffers of a captured step: the rows are copied into them and
         the batch is built on them, asking for every row (the caller picks the wanted ones from the captured output)."""
-        rows, toks, want, base, max_kv = [[], [], [], [], []], [], [], 0, 0
+        rows, toks, want, base, max_kv = [[], [], [], [], [], [], [], [], []], [], [], 0, 0
         for seq_id, tokens, w in entries:
             s = self.open(seq_id)
             n = len(tokens)
             start = self.extend(s, n)
             rd, wr = self.state_rows(s, start)
+            for r, v in zip(rows[5:], (base, n, rd, wr)):
+                r.append(v)
             rows[0] += range(start, start + n)
             rows[1] += [s] * n
             rows[2] += [-1] + list(range(base, base + n - 1))
@@ -215,12 +227,15 @@ class PagedStateCache:
             want += [base + i for i in (range(n) if want_all else w)]
             base += n
             max_kv = max(max_kv, start + n)
+        n_seqs = len(rows[5])
+        for r in rows[5:]:
+            r += [0] * (base - n_seqs)
         self.sync_table()
         if static is not None:
             static[0].copy_(torch.tensor(rows, dtype=torch.int32))
             static[1].copy_(torch.tensor(toks, dtype=torch.int64))
-            b = ForwardBatch(static[0], static[1], torch.tensor(want, dtype=torch.int64).to(self.device, non_blocking=True), self.capacity_per_sequence())
+            b = ForwardBatch(static[0], static[1], torch.tensor(want, dtype=torch.int64).to(self.device, non_blocking=True), self.capacity_per_sequence(), n_seqs)
             return b
         meta = torch.tensor(rows, dtype=torch.int32).to(self.device, non_blocking=True)
         return ForwardBatch(meta, torch.tensor(toks, dtype=torch.int64).to(self.device, non_blocking=True),
-                            torch.tensor(want, dtype=torch.int64).to(self.device, non_blocking=True), max_kv)
+                            torch.tensor(want, dtype=torch.int64).to(self.device, non_blocking=True), max_kv, n_seqs)

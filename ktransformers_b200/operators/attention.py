@@ -8,6 +8,7 @@ TMEM + TMA, csrc/mla.cu); the cache write is ktb200_mla_kv_write; the projection
 GEMVs over the bf16 halves of kv_b_proj; torch.matmul for other dtypes).  Prefill (q_len > 1 without absorb) is outside this path and raises."""
 from __future__ import annotations
 
+import math
 from typing import Optional, Tuple
 
 import torch
@@ -187,3 +188,92 @@ class KLatentWindowAttention(torch.nn.Module):
         og = torch.empty((T, s.heads * s.vdim), dtype=dt, device=dev)
         native.check_seq(lib.ktb200_sigmoid_gate_mul(o.data_ptr(), proj[:, s.q_rank + s.kv_rank + s.rot_dim:].data_ptr(), self.n_in, og.data_ptr(), T, s.heads, s.vdim, code, st))
         return torch.nn.functional.linear(og, self.o)
+
+
+def distance_bias_table(rel: torch.Tensor, bias_max: float) -> torch.Tensor:
+    """A learned bias per (distance bucket, head), expanded to one row per DISTANCE: rows 0 .. n - 1 with n - 1 the first
+    distance whose bucket is the last one, so a kernel indexes `min(i - j, n - 1)`.  With B rows in `rel` and half = B // 2:
+    bucket(n) = n below half, else min(B - 1, half + floor(ln(n / half) / ln(bias_max / half) * (B - half))) — exact below half,
+    logarithmic up to `bias_max`, constant beyond."""
+    B = rel.shape[0]
+    half = B // 2
+    buckets, n = [], 0
+    while True:
+        b = n if n < half else min(B - 1, half + int(math.floor(math.log(n / half) / math.log(bias_max / half) * (B - half))))
+        buckets.append(b)
+        if b == B - 1 and n >= half:
+            break
+        n += 1
+    return rel.float().index_select(0, torch.tensor(buckets, dtype=torch.int64, device=rel.device)).contiguous()
+
+
+class KSigmoidBiasAttention(torch.nn.Module):
+    """Causal attention without a soft-max over grouped key/value heads: the weight of key j for query i of head h is
+
+        sigmoid(scale * q_i . k_j + rel[bucket(i - j)][h] + pb[h])          (not normalised over the keys)
+
+    with per-head RMS norms of queries and keys (one weight per norm, shared by the heads), no rotation, a query temperature
+    `1 + coef * ln(floor((pos + 1) / every) + 1)`, and one sigmoid output gate per head read from the mixer's input.
+
+        P     = [W_q ; W_k ; W_v ; W_g] h + b                  one GEMM over the matrices that read the mixer input
+        q, k  -> norms, temperature; [k | v] -> paged cache    ktb200_qk_norm_cache_write
+        o_h   = sum_j weight_ij v_j * sigmoid(g_h)             ktb200_sigmoid_bias_attn (fp32 scores and weights)
+        out   = W_o o + b_o                                    GEMM
+
+    Sizes, scale, the bias table's reach and the temperature constants are constructor parameters
+    (models/configuration_mabidra.SigmoidAttentionSpec).  `cache_idx` picks the cache layer, so one set of weights can run
+    several times per step with separate caches."""
+
+    def __init__(self, width: int, spec, eps: float, dtype=torch.bfloat16, device="cuda"):
+        super().__init__()
+        P = lambda *shape, dt=dtype: torch.nn.Parameter(torch.zeros(shape, dtype=dt, device=device), requires_grad=False)
+        s = self.spec = spec
+        if s.heads % s.kv_heads:
+            raise ValueError("query heads must divide into the key/value heads")
+        self.width, self.eps = width, eps
+        self.n_q, self.n_kv = s.heads * s.dim, s.kv_heads * (s.dim + s.vdim)
+        self.n_in = (self.n_q + self.n_kv + s.heads + 7) // 8 * 8       # rows padded so that every row of P starts 16-byte aligned
+        self.w_in, self.b_in = P(self.n_in, width), P(self.n_in)
+        self.q_norm, self.k_norm = P(s.dim), P(s.dim)
+        self.head_bias = P(s.heads, dt=torch.float32)
+        self.o, self.o_b = P(width, s.heads * s.vdim), P(width)
+        self.register_buffer("bias_table", torch.zeros((1, s.heads), dtype=torch.float32, device=device), persistent=False)
+
+    def load(self, loader, prefix: str):
+        s, t = self.spec, lambda n: loader.load_tensor(prefix + n, "cpu")
+        rows = self.n_q + self.n_kv + s.heads
+        self.w_in.data[:rows].copy_(torch.cat([t("q"), t("k"), t("v"), t("g")], 0))
+        self.b_in.data[:self.n_q + self.n_kv].copy_(torch.cat([t("q.b"), t("k.b"), t("v.b")], 0))
+        self.q_norm.data.copy_(t("q.norm"))
+        self.k_norm.data.copy_(t("k.norm"))
+        self.head_bias.data.copy_(t("pb").float())
+        self.o.data.copy_(t("o"))
+        self.o_b.data.copy_(t("o.b"))
+        self.bias_table = distance_bias_table(t("rel"), s.bias_max).to(self.w_in.device)
+
+    def pick_splits(self, n_tokens: int, max_kv: int) -> int:
+        """Cut the key range when a small batch would leave most SMs idle on a long context."""
+        s = self.spec
+        ctas = n_tokens * s.kv_heads * ((s.heads // s.kv_heads + 7) // 8)
+        if ctas >= 148 or max_kv <= 256:
+            return 1
+        return max(1, min(64, max_kv // 128, 592 // ctas))
+
+    def forward(self, h: torch.Tensor, batch, cache, cache_idx: int) -> torch.Tensor:
+        s, T, dev, dt = self.spec, h.shape[0], h.device, h.dtype
+        lib, code, st = native.seq_lib(), native.GGML_BF16 if dt == torch.bfloat16 else native.GGML_F32, torch.cuda.current_stream(h.device).cuda_stream
+        kv = cache.key_cache[cache_idx]
+        proj = torch.nn.functional.linear(h, self.w_in, self.b_in)
+        q = torch.empty((T, s.heads, s.dim), dtype=dt, device=dev)
+        native.check_seq(lib.ktb200_qk_norm_cache_write(proj.data_ptr(), self.n_in, s.heads, s.kv_heads, s.dim, s.vdim, self.q_norm.data_ptr(), self.k_norm.data_ptr(),
+                                                        float(self.eps), float(s.temp_coef), int(s.temp_every), batch.pos.data_ptr(), batch.slot.data_ptr(),
+                                                        cache.page_table.data_ptr(), cache.max_pages_per_seq, cache.page_size, kv.data_ptr(), q.data_ptr(), T, code, st))
+        gate = proj[:, self.n_q + self.n_kv:]
+        o = torch.empty((T, s.heads * s.vdim), dtype=dt, device=dev)
+        splits = self.pick_splits(T, batch.max_kv)
+        ws = torch.empty(lib.ktb200_sigmoid_bias_attn_workspace(T, s.heads, s.vdim, splits) // 4, dtype=torch.float32, device=dev) if splits > 1 else None
+        native.check_seq(lib.ktb200_sigmoid_bias_attn(q.data_ptr(), s.heads, s.kv_heads, s.dim, s.vdim, float(s.scale), self.bias_table.data_ptr(), self.bias_table.shape[0],
+                                                      self.head_bias.data_ptr(), batch.pos.data_ptr(), batch.slot.data_ptr(), cache.page_table.data_ptr(),
+                                                      cache.max_pages_per_seq, cache.page_size, kv.data_ptr(), gate.data_ptr(), self.n_in, o.data_ptr(), T, splits,
+                                                      ws.data_ptr() if ws is not None else None, code, st))
+        return torch.nn.functional.linear(o, self.o, self.o_b)

@@ -542,17 +542,19 @@ class KExpertsDense(nn.Module):
     by_expert_rows = 4              # most pairs whose rows such a kernel keeps in shared memory at a time
     by_expert_staged = 0            # 2 or 4 to fix that number; 0: the library chooses from the batch
 
-    def __init__(self, width: int, ff: int, experts: int, dtype=torch.bfloat16, device="cuda"):
+    def __init__(self, width: int, ff: int, experts: int, dtype=torch.bfloat16, device="cuda", gated: bool = True):
+        """`gated=False`: experts of two matrices, `W_down relu(W_up x)^2`, run by the same kernels without a gate matrix."""
         super().__init__()
-        self.width, self.ff, self.experts = width, ff, experts
-        self.gate = nn.Parameter(torch.empty((experts, ff, width), dtype=dtype, device=device), requires_grad=False)
+        self.width, self.ff, self.experts, self.gated = width, ff, experts, gated
+        self.gate = nn.Parameter(torch.empty((experts, ff, width), dtype=dtype, device=device), requires_grad=False) if gated else None
         self.up = nn.Parameter(torch.empty((experts, ff, width), dtype=dtype, device=device), requires_grad=False)
         self.down = nn.Parameter(torch.empty((experts, width, ff), dtype=dtype, device=device), requires_grad=False)
 
     def load(self, loader, prefix: str, names=("gate", "up", "down")):
         for e in range(self.experts):
             for p, n in zip((self.gate, self.up, self.down), names):
-                p.data[e].copy_(loader.load_tensor(f"{prefix}e{e}.{n}", "cpu"))
+                if p is not None:
+                    p.data[e].copy_(loader.load_tensor(f"{prefix}e{e}.{n}", "cpu"))
 
     def grouped_is_device_only(self, dtype) -> bool:
         """whether the grouped path runs as the library's grouped GEMM, which takes the segment ends on the device (no host read)"""
@@ -574,7 +576,7 @@ class KExpertsDense(nn.Module):
             return True
         if not self.grouped_is_device_only(dtype):
             return False
-        all_bytes = 3.0 * self.experts * self.ff * self.width * 2
+        all_bytes = (3.0 if self.gated else 2.0) * self.experts * self.ff * self.width * 2
         passes = T * top / (4.0 * self.experts) + 0.5
         return (passes - 1.0) * all_bytes / 5e12 > 300e-6
 
@@ -589,14 +591,15 @@ class KExpertsDense(nn.Module):
         act = torch.empty((T * top, self.ff), dtype=x.dtype, device=x.device)
         out = torch.empty((T, self.width), dtype=torch.float32, device=x.device)
         lib, dt, st = native.seq_lib(), TORCH_TO_GGML_HIDDEN[x.dtype], _stream(x.device)
+        gate_ptr = self.gate.data_ptr() if self.gated else None
         if by_expert:
             pair_rows = torch.empty((T * top, self.width), dtype=torch.float32, device=x.device)
-            native.check_seq(lib.ktb200_experts_gate_up_by_expert(x.data_ptr(), ids.data_ptr(), top, self.experts, self.gate.data_ptr(), self.up.data_ptr(),
+            native.check_seq(lib.ktb200_experts_gate_up_by_expert(x.data_ptr(), ids.data_ptr(), top, self.experts, gate_ptr, self.up.data_ptr(),
                                                                   act.data_ptr(), T, self.width, self.ff, self.by_expert_staged, dt, st))
             native.check_seq(lib.ktb200_experts_down_by_expert(act.data_ptr(), ids.data_ptr(), weights.data_ptr(), top, self.experts, self.down.data_ptr(),
                                                                pair_rows.data_ptr(), out.data_ptr(), T, self.width, self.ff, self.by_expert_staged, dt, st))
             return out
-        native.check_seq(lib.ktb200_experts_gate_up(x.data_ptr(), ids.data_ptr(), top, self.gate.data_ptr(), self.up.data_ptr(), act.data_ptr(), T, self.width,
+        native.check_seq(lib.ktb200_experts_gate_up(x.data_ptr(), ids.data_ptr(), top, gate_ptr, self.up.data_ptr(), act.data_ptr(), T, self.width,
                                                     self.ff, dt, st))
         native.check_seq(lib.ktb200_experts_down(act.data_ptr(), ids.data_ptr(), weights.data_ptr(), top, self.down.data_ptr(), out.data_ptr(), T, self.width,
                                                  self.ff, dt, st))
@@ -613,16 +616,18 @@ class KExpertsDense(nn.Module):
         if x.dtype == torch.bfloat16 and self.width % 8 == 0 and self.ff % 8 == 0 and hasattr(F, "grouped_mm"):
             # the library's grouped GEMM takes the segment ends on the device: no host read of the routing, three launches
             offs = counts.cumsum(0).to(torch.int32)
-            g, u = F.grouped_mm(xs, self.gate.transpose(1, 2), offs=offs).float(), F.grouped_mm(xs, self.up.transpose(1, 2), offs=offs).float()
-            y = F.grouped_mm((F.silu(g) * u).to(x.dtype), self.down.transpose(1, 2), offs=offs)
+            u = F.grouped_mm(xs, self.up.transpose(1, 2), offs=offs).float()
+            a = F.silu(F.grouped_mm(xs, self.gate.transpose(1, 2), offs=offs).float()) * u if self.gated else torch.relu(u).square()
+            y = F.grouped_mm(a.to(x.dtype), self.down.transpose(1, 2), offs=offs)
         else:
             y = torch.empty((T * top, self.width), dtype=x.dtype, device=x.device)
             lo = 0
             for e, n in enumerate(counts.tolist()):                              # one host read of a step's routing
                 if n:
                     seg = xs[lo:lo + n]
-                    g, u = F.linear(seg, self.gate[e]).float(), F.linear(seg, self.up[e]).float()
-                    y[lo:lo + n] = F.linear((F.silu(g) * u).to(x.dtype), self.down[e])
+                    u = F.linear(seg, self.up[e]).float()
+                    a = F.silu(F.linear(seg, self.gate[e]).float()) * u if self.gated else torch.relu(u).square()
+                    y[lo:lo + n] = F.linear(a.to(x.dtype), self.down[e])
                     lo += n
         pairs = torch.empty_like(y)
         pairs[order] = y
@@ -641,6 +646,25 @@ class KSoftmaxTopKMoE(nn.Module):
     def load(self, loader, prefix: str):
         self.router.load(loader, prefix + "router")
         self.experts.load(loader, prefix)
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        ids, w = self.router(h)
+        return self.experts(h, ids, w)
+
+
+class KTopKSoftmaxMoE(nn.Module):
+    """router (operators/gate.KTopKSoftmaxGate: biased logits, top-k, soft-max over the chosen) -> dense experts without a gate
+    matrix (relu squared): a mixture-of-experts feed-forward without shared experts."""
+
+    def __init__(self, width: int, ff: int, experts: int, top: int, dtype=torch.bfloat16, device="cuda"):
+        super().__init__()
+        from .gate import KTopKSoftmaxGate
+        self.router = KTopKSoftmaxGate(width, experts, top, device=device)
+        self.experts = KExpertsDense(width, ff, experts, dtype=dtype, device=device, gated=False)
+
+    def load(self, loader, prefix: str):
+        self.router.load(loader, prefix + "router")
+        self.experts.load(loader, prefix, names=(None, "up", "down"))
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         ids, w = self.router(h)

@@ -16,7 +16,7 @@ from .. import native
 from ..util.custom_gguf import TORCH_TO_GGML_HIDDEN
 from .base_operator import BaseInjectedModule
 
-_SCORING = {"sigmoid": 0, "softmax": 1}
+_SCORING = {"sigmoid": 0, "softmax": 1, "topk_softmax": 2}
 _TOPK = {"noaux_tc": 0, "greedy": 1, "group_limited_greedy": 2}
 
 
@@ -121,6 +121,38 @@ class KSoftmaxTopKGate(nn.Module):
         wt = torch.empty((n, self.top), dtype=torch.float32, device=x.device)
         cfg = native.GateConfig(self.experts, self.width, self.top, 1, 1, _SCORING["softmax"], _TOPK["greedy"], 0, 1.0, self.weight.data_ptr(), None,
                                 TORCH_TO_GGML_HIDDEN[x.dtype])
+        native.check_seq(native.seq_lib().ktb200_moe_gate_forward(C.byref(cfg), n, x.data_ptr(), idx.data_ptr(), wt.data_ptr(), None, None,
+                                                                  torch.cuda.current_stream(x.device).cuda_stream))
+        return idx, wt
+
+
+class KTopKSoftmaxGate(nn.Module):
+    """Logits `W x + b` in fp32, the `top` largest chosen, weights = soft-max over the chosen logits only (so one chosen expert
+    weighs 1): the router kernel's `scoring = topk_softmax` case, where the bias belongs to the logits.  As for
+    KSoftmaxTopKGate, batches from `gemm_min_tokens` tokens run an fp32 library GEMM (TF32 off) and torch's top-k."""
+
+    gemm_min_tokens = 48
+
+    def __init__(self, width: int, experts: int, top: int, device="cuda"):
+        super().__init__()
+        self.width, self.experts, self.top = width, experts, top
+        self.weight = nn.Parameter(torch.empty((experts, width), dtype=torch.float32, device=device), requires_grad=False)
+        self.bias = nn.Parameter(torch.zeros(experts, dtype=torch.float32, device=device), requires_grad=False)
+
+    def load(self, loader, key: str):
+        self.weight.data.copy_(loader.load_tensor(key, "cpu").float())
+        self.bias.data.copy_(loader.load_tensor(key + ".b", "cpu").float())
+
+    def forward(self, x: torch.Tensor):
+        n = x.shape[0]
+        kernel_fits = self.width % 4 == 0 and self.experts <= 512 and self.top <= 32
+        if n >= self.gemm_min_tokens or not kernel_fits:
+            val, idx = torch.topk(torch.addmm(self.bias, x.float(), self.weight.t()), self.top, dim=-1)
+            return idx, torch.softmax(val, dim=-1).contiguous()
+        idx = torch.empty((n, self.top), dtype=torch.int64, device=x.device)
+        wt = torch.empty((n, self.top), dtype=torch.float32, device=x.device)
+        cfg = native.GateConfig(self.experts, self.width, self.top, 1, 1, _SCORING["topk_softmax"], _TOPK["greedy"], 1, 1.0, self.weight.data_ptr(),
+                                self.bias.data_ptr(), TORCH_TO_GGML_HIDDEN[x.dtype])
         native.check_seq(native.seq_lib().ktb200_moe_gate_forward(C.byref(cfg), n, x.data_ptr(), idx.data_ptr(), wt.data_ptr(), None, None,
                                                                   torch.cuda.current_stream(x.device).cuda_stream))
         return idx, wt

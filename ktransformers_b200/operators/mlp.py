@@ -33,3 +33,32 @@ class KPolyNormMLP(nn.Module):
         native.check_seq(native.seq_lib().ktb200_poly_norm(z.data_ptr(), a.data_ptr(), self.coef.data_ptr(), float(self.eps), z.shape[0], self.ff,
                                                            GGML_OF[z.dtype], torch.cuda.current_stream(z.device).cuda_stream))
         return F.linear(a, self.down)
+
+
+class KXIELUMLP(nn.Module):
+    """A two-matrix feed-forward with the xIELU activation, a quadratic above zero and a saturating exponential below:
+
+        z = W_up h ;  act(z) = sp(p) z^2 + z/2            (z > 0)
+                      act(z) = (1/2 + sp(q)) (e^z - 1 - z) + z/2   (z <= 0) ,  sp = softplus ;  W_down act
+
+    The two products are library GEMMs; the activation is one `ktb200_xielu` launch (csrc/seq_mixers.cu, fp32 inside, softplus
+    of the two learned numbers on the device)."""
+
+    def __init__(self, width: int, ff: int, dtype=torch.bfloat16, device="cuda"):
+        super().__init__()
+        self.width, self.ff = width, ff
+        self.up = nn.Parameter(torch.empty((ff, width), dtype=dtype, device=device), requires_grad=False)
+        self.down = nn.Parameter(torch.empty((width, ff), dtype=dtype, device=device), requires_grad=False)
+        self.pq = nn.Parameter(torch.zeros(2, dtype=torch.float32, device=device), requires_grad=False)
+
+    def load(self, loader, prefix: str):
+        self.up.data.copy_(loader.load_tensor(prefix + "up", "cpu"))
+        self.down.data.copy_(loader.load_tensor(prefix + "down", "cpu"))
+        self.pq.data.copy_(loader.load_tensor(prefix + "act", "cpu").float())
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        z = F.linear(h, self.up)
+        a = torch.empty_like(z)
+        native.check_seq(native.seq_lib().ktb200_xielu(z.data_ptr(), a.data_ptr(), self.pq.data_ptr(), z.numel(), GGML_OF[z.dtype],
+                                                       torch.cuda.current_stream(z.device).cuda_stream))
+        return F.linear(a, self.down)

@@ -57,3 +57,38 @@ class KGroupRMSNormShift(nn.Module):
             _ptr(batch.wr_row) if hs is not None else None, _ptr(state) if hs is not None else None, _ptr(h), _ptr(hs), T, self.width, GGML_OF[dt],
             torch.cuda.current_stream(x.device).cuda_stream))
         return x_out, h, hs
+
+
+class KGroupRMSNorm(nn.Module):
+    """One grouped RMS norm weight of a layer that norms BOTH sides of every sublayer, `x <- x + post(sublayer(pre(x)))`.
+    The norms never run alone: `KGroupRMSNorm.fused` is one `ktb200_group_rmsnorm_sandwich` launch (csrc/seq_mixers.cu) for
+
+        x_out = x_in + gnorm(y) * post.weight + row       the sublayer's output y normed and added to the fp32 residual
+        h     = gnorm(x_out) * pre.weight                  the NEXT sublayer's input, rounded once to the compute dtype
+
+    with every term optional (no x_in / post: the stream restarts from y; no pre: nothing follows)."""
+
+    def __init__(self, width: int, groups: int, eps: float, dtype=torch.bfloat16, device="cuda"):
+        super().__init__()
+        if width % groups:
+            raise ValueError("the width must divide into the norm groups")
+        self.width, self.groups, self.eps = width, groups, eps
+        self.weight = nn.Parameter(torch.ones(width, dtype=dtype, device=device), requires_grad=False)
+
+    def load(self, loader, key: str):
+        self.weight.data.copy_(loader.load_tensor(key, "cpu"))
+
+    @staticmethod
+    def fused(x_in: Optional[torch.Tensor], y: torch.Tensor, post: Optional["KGroupRMSNorm"], pre: Optional["KGroupRMSNorm"], row_add: Optional[torch.Tensor] = None,
+              keep_x: bool = True):
+        """x_in [T, width] fp32 or None, y [T, width] fp32 or the compute dtype.  Returns (x_out fp32 or None, h or None)."""
+        ref = pre if pre is not None else post
+        T, D = y.shape
+        assert y.is_contiguous() and (x_in is None or x_in.is_contiguous()) and D == ref.width
+        dt = ref.weight.dtype
+        x_out = torch.empty((T, D), dtype=torch.float32, device=y.device) if keep_x or pre is None else None
+        h = torch.empty((T, D), dtype=dt, device=y.device) if pre is not None else None
+        native.check_seq(native.seq_lib().ktb200_group_rmsnorm_sandwich(
+            _ptr(x_in), y.data_ptr(), GGML_OF[y.dtype], post.weight.data_ptr() if post is not None else None, _ptr(row_add), _ptr(x_out),
+            pre.weight.data_ptr() if pre is not None else None, _ptr(h), ref.groups, float(ref.eps), T, D, GGML_OF[dt], torch.cuda.current_stream(y.device).cuda_stream))
+        return x_out, h

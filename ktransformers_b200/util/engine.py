@@ -48,14 +48,14 @@ class _CapturedStep:
 
     def __init__(self, model, cache, n: int):
         dev = cache.device
-        self.meta = torch.zeros((5, n), dtype=torch.int32, device=dev)
+        self.meta = torch.zeros((9, n), dtype=torch.int32, device=dev)
         self.tokens = torch.zeros(n, dtype=torch.int64, device=dev)
         self.all_rows = torch.arange(n, dtype=torch.int64, device=dev)
         self.graph, self.logits = None, None
 
     def capture(self, model, cache):
         from ..models.custom_cache import ForwardBatch
-        batch = ForwardBatch(self.meta, self.tokens, self.all_rows, cache.capacity_per_sequence())
+        batch = ForwardBatch(self.meta, self.tokens, self.all_rows, cache.capacity_per_sequence(), self.meta.shape[1])
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
             self.logits = model(batch, cache)
