@@ -404,6 +404,38 @@ int ktb200_experts_gate_up_by_expert(const void* x, const int64_t* ids, int top,
                                      int n_tokens, int width, int ff, int staged, int dtype, void* stream);
 int ktb200_experts_down_by_expert(const void* act, const int64_t* ids, const float* weights, int top, int n_experts, const void* w_down,
                                   float* pair_rows, float* out, int n_tokens, int width, int ff, int staged, int dtype, void* stream);
+/* w_gate == NULL in the four calls above: experts of two matrices, act = relu(W_up x)^2.
+ *
+ * Layers with norms on both sides of every sublayer, sigmoid attention and gated linear attention (csrc/seq_mixers.cu):
+ *   ktb200_group_rmsnorm_sandwich   x_out = x_in + gnorm(y) * w_post + row_add ; h = gnorm(x_out) * w_pre.  x_in, w_post, row_add,
+ *                                   x_out (when w_pre is given) and w_pre / h_out may be NULL; y is fp32 or bf16 (y_type).
+ *   ktb200_qk_norm_cache_write      proj rows [q H*d | k G*d | v G*dv | ...]: per-head RMS norm of q and k, q times
+ *                                   1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1), [k | v] into the paged cache, q into q_out
+ *   ktb200_sigmoid_bias_attn        out[t][h] = sigmoid(gate[t][h]) * sum_{j <= pos} sigmoid(scale q.k_j + bias[min(pos - j, n_bias - 1)][h]
+ *                                   + head_bias[h]) v_j ; query head h reads key/value head h / (H / G); splits > 1 cuts the key range
+ *                                   (workspace: ktb200_sigmoid_bias_attn_workspace bytes)
+ *   ktb200_gla_scan                 per sequence portion seqs[0..3][s] = (first row, rows, state row to read or -1, state row to write or -1):
+ *                                   S <- diag(a_t) S + k_t v_t^T, o_t = S^T q_t / sqrt(dim), a = sigmoid(z + z_bias)^(1 / tau); state rows
+ *                                   [heads][dim][vdim] fp32; q / k / v at column offsets of proj; dim <= 256
+ *   ktb200_gla_out                  out = o / sqrt(mean_vdim(o^2) + eps) * norm_w * silu(gate)
+ *   ktb200_xielu                    z > 0: softplus(pq[0]) z^2 + z/2 ; else (1/2 + softplus(pq[1])) (exp(z) - 1 - z) + z/2 */
+int ktb200_group_rmsnorm_sandwich(const float* x_in, const void* y, int y_type, const void* w_post, const float* row_add, float* x_out,
+                                  const void* w_pre, void* h_out, int groups, float eps, int n_tokens, int width, int dtype, void* stream);
+int ktb200_qk_norm_cache_write(const void* proj, long proj_stride, int heads, int kv_heads, int dim, int vdim, const void* q_norm_w,
+                               const void* k_norm_w, float eps, float temp_coef, int temp_every, const int* pos, const int* slot,
+                               const int* page_table, int max_pages, int page_size, void* cache, void* q_out, int n_tokens, int dtype,
+                               void* stream);
+size_t ktb200_sigmoid_bias_attn_workspace(int n_tokens, int heads, int vdim, int splits);
+int ktb200_sigmoid_bias_attn(const void* q, int heads, int kv_heads, int dim, int vdim, float scale, const float* bias, int n_bias,
+                             const float* head_bias, const int* pos, const int* slot, const int* page_table, int max_pages, int page_size,
+                             const void* cache, const void* gate, long gate_stride, void* out, int n_tokens, int splits, float* workspace,
+                             int dtype, void* stream);
+int ktb200_gla_scan(const void* proj, long proj_stride, int q_off, int k_off, int v_off, const void* z, long z_stride, const void* z_bias,
+                    float tau, int heads, int dim, int vdim, const int* seqs, int seqs_stride, int n_seqs, float* state, float* o_out,
+                    int dtype, void* stream);
+int ktb200_gla_out(const float* o, const void* norm_w, float eps, const void* gate, long gate_stride, void* out, int n_tokens, int heads,
+                   int vdim, int dtype, void* stream);
+int ktb200_xielu(const void* z, void* out, const float* pq, long n, int dtype, void* stream);
 
 /* Diagnostics (bench.py --probe): time a plain read-only stream over `bytes` of device memory.
  * mode 0 = grid-stride coalesced 16-byte loads; mode 1 = every warp reads chunk_bytes pieces at hashed offsets
