@@ -411,7 +411,7 @@ int ktb200_experts_down_by_expert(const void* act, const int64_t* ids, const flo
  *                                   x_out (when w_pre is given) and w_pre / h_out may be NULL; y is fp32 or bf16 (y_type).
  *   ktb200_qk_norm_cache_write      proj rows [q H*d | k G*d | v G*dv | ...]: per-head RMS norm of q and k, q times
  *                                   1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1), [k | v] into the paged cache, q into q_out
- *   ktb200_sigmoid_bias_attn        out[t][h] = sigmoid(gate[t][h]) * sum_{j <= pos} sigmoid(scale q.k_j + bias[min(pos - j, n_bias - 1)][h]
+ *   ktb200_sigmoid_bias_attn        out[t][h] = sigmoid(gate[t][h]) * sum_{j <= pos} sigmoid(scale q.k_j + bias[h][min(pos - j, n_bias - 1)]
  *                                   + head_bias[h]) v_j ; query head h reads key/value head h / (H / G); splits > 1 cuts the key range
  *                                   (workspace: ktb200_sigmoid_bias_attn_workspace bytes)
  *   ktb200_gla_scan                 per sequence portion seqs[0..3][s] = (first row, rows, state row to read or -1, state row to write or -1):
@@ -427,9 +427,13 @@ int ktb200_qk_norm_cache_write(const void* proj, long proj_stride, int heads, in
                                void* stream);
 size_t ktb200_sigmoid_bias_attn_workspace(int n_tokens, int heads, int vdim, int splits);
 int ktb200_sigmoid_bias_attn(const void* q, int heads, int kv_heads, int dim, int vdim, float scale, const float* bias, int n_bias,
-                             const float* head_bias, const int* pos, const int* slot, const int* page_table, int max_pages, int page_size,
-                             const void* cache, const void* gate, long gate_stride, void* out, int n_tokens, int splits, float* workspace,
-                             int dtype, void* stream);
+                             const float* head_bias, const int* pos, const int* slot, const int* seqs, int seqs_stride, int n_seqs,
+                             const int* page_table, int max_pages, int page_size, const void* cache, const void* gate, long gate_stride, void* out,
+                             int n_tokens, int splits, float* workspace, int dtype, int allow_tensor_cores, void* stream);
+/* whether that call runs tensor-core tiles (bf16, dim and vdim multiples of 16 up to 128, seqs given), and an upper bound of its
+ * row tiles per key/value head (for choosing splits) */
+int ktb200_sigmoid_bias_attn_uses_tensor_cores(int heads, int kv_heads, int dim, int vdim, int dtype);
+int ktb200_sigmoid_bias_attn_tiles(int heads, int kv_heads, int n_tokens, int n_seqs);
 int ktb200_gla_scan(const void* proj, long proj_stride, int q_off, int k_off, int v_off, const void* z, long z_stride, const void* z_bias,
                     float tau, int heads, int dim, int vdim, const int* seqs, int seqs_stride, int n_seqs, float* state, float* o_out,
                     int dtype, void* stream);

@@ -4,8 +4,9 @@
 //   ktb200_group_rmsnorm_sandwich  x_out = x_in + gnorm(y) * w_post + row   then   h = gnorm(x_out) * w_pre
 //                                  (gnorm: RMS norm in `groups` equal consecutive parts; every term optional)
 //   ktb200_qk_norm_cache_write     per-head RMS norm of queries and keys, query temperature by position, paged write of [k | v]
-//   ktb200_sigmoid_bias_attn       o_i = sum_{j <= i} sigmoid(scale q_i.k_j + bias[min(i - j, n - 1)][h] + pb[h]) v_j over the paged
-//                                  cache, grouped query heads, times sigmoid(gate[i][h]); key range cut into splits for few tokens
+//   ktb200_sigmoid_bias_attn       o_i = sum_{j <= i} sigmoid(scale q_i.k_j + bias[h][min(i - j, n - 1)] + pb[h]) v_j over the paged
+//                                  cache, grouped query heads, times sigmoid(gate[i][h]); key range cut into splits for few tokens;
+//                                  bf16 with head sizes that are multiples of 16 up to 128: m16n8k16 tensor-core tiles
 //   ktb200_gla_scan                S_t = diag(a_t) S_{t-1} + k_t v_t^T, o_t = S_t^T q_t per sequence portion, state rows in fp32,
 //                                  a_t = sigmoid(z_t + b)^(1/tau)
 //   ktb200_gla_out                 per-head RMS norm of o times silu(gate)
@@ -138,7 +139,7 @@ __global__ void __launch_bounds__(256) sigmoid_attn_kernel(const T* __restrict__
     if (k_lo < k_hi) {
         if (live) {
             for (int i = lane; i < d; i += 32) qs[warp * d + i] = to_f(q[(t * H + h) * d + i]) * scale;
-            for (int i = lane; i < n_bias; i += 32) bs[warp * n_bias + i] = bias[(long)i * H + h] + pb[h];
+            for (int i = lane; i < n_bias; i += 32) bs[warp * n_bias + i] = bias[(long)h * n_bias + i] + pb[h];
         }
         const int* pt = page_table + (long)slot[t] * max_pages;
         const long cw = (long)G * (d + dv);
@@ -183,6 +184,188 @@ __global__ void __launch_bounds__(256) sigmoid_attn_kernel(const T* __restrict__
 #pragma unroll
         for (int c = 0; c < kAttnMaxCols; c++)
             if (lane + 32 * c < dv) out[(t * H + h) * dv + lane + 32 * c] = from_f<T>(acc[c] * gt);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ sigmoid attention, tensor cores (bf16)
+// A CTA of 4 warps owns a tile of 64 rows = (token, query head) pairs of ONE sequence portion and ONE key/value head: `RH` query
+// heads of the group for each of 64 / RH consecutive tokens (prompt portions fill the rows with tokens, decode steps with the
+// group's heads).  Keys run in tiles of 64 through a two-stage cp.async ring of [k | v] rows gathered through the page table;
+// S = Q K^T and O += P V are m16n8k16 bf16 MMAs with fp32 accumulators; the scores are scaled, biased and pushed through the
+// sigmoid in fp32 registers and handed to the second product as bf16.  No running maximum and no rescaling: the weights are
+// not normalised.  grid (tile bound, G * head blocks, splits); tiles are found from the per-sequence rows `seqs`.
+constexpr int kMmaRows = 64, kMmaKeys = 64, kMmaPad = 8;
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+    const unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
+    const int sz = valid ? 16 : 0;      // 0: the 16 bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(sa), "l"(gmem), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+    const unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(sa));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem) {
+    const unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(sa));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ float sigmoid_fast(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
+
+template <int D16MAX, int DV16MAX>
+__global__ void __launch_bounds__(128) sigmoid_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, int H, int G, int d, int dv, float scale, const float* __restrict__ biasT,
+                                                               int n_bias, const float* __restrict__ pb, const int* __restrict__ pos, const int* __restrict__ slot,
+                                                               const int* __restrict__ seqs, int seqs_stride, int n_seqs, int RH, const int* __restrict__ page_table,
+                                                               int max_pages, int page_size, const __nv_bfloat16* __restrict__ cache,
+                                                               const __nv_bfloat16* __restrict__ gate, long gate_stride, __nv_bfloat16* __restrict__ out,
+                                                               float* __restrict__ partial, int n_tokens) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ int tile_info[3];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gq = lane >> 2, tq = lane & 3;
+    const int TOKS = kMmaRows / RH;
+    if (tid == 0) {      // which sequence portion and which of its tokens this tile covers
+        int b = blockIdx.x, found = -1, off = 0, len = 0;
+        for (int s = 0; s < n_seqs; s++) {
+            len = seqs[seqs_stride + s];
+            const int nt = (len + TOKS - 1) / TOKS;
+            if (b < nt) { found = s; off = b * TOKS; break; }
+            b -= nt;
+        }
+        tile_info[0] = found;
+        tile_info[1] = found >= 0 ? seqs[found] + off : 0;
+        tile_info[2] = found >= 0 ? min(TOKS, len - off) : 0;
+    }
+    __syncthreads();
+    if (tile_info[0] < 0) return;
+    const int tok0 = tile_info[1], ntok = tile_info[2];
+    const int R = H / G, hblocks = R / RH;
+    const int g = blockIdx.y / hblocks, h0 = g * R + (blockIdx.y % hblocks) * RH;
+    const int d16 = d >> 4, dv16 = dv >> 4, ldk = d + kMmaPad, ldv = dv + kMmaPad;
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+    __nv_bfloat16* Ks = Qs + kMmaRows * ldk;                 // [2][64][ldk]
+    __nv_bfloat16* Vs = Ks + 2 * kMmaKeys * ldk;             // [2][64][ldv]
+    const int pos0 = pos[tok0], max_pos = pos0 + ntok - 1;
+    const int splits = gridDim.z, n_keys = max_pos + 1;
+    const int per = ((n_keys + splits - 1) / splits + kMmaKeys - 1) / kMmaKeys * kMmaKeys;
+    const int k_lo = blockIdx.z * per, k_hi = min(n_keys, k_lo + per);
+    // this thread's two rows of the warp's 16
+    const int rA = warp * 16 + gq, rB = rA + 8;
+    const int tokA = rA / RH, tokB = rB / RH, hA = h0 + rA % RH, hB = h0 + rB % RH;
+    const bool vA = tokA < ntok, vB = tokB < ntok;
+    const int pA = pos0 + tokA, pB = pos0 + tokB;
+    const bool warp_live = (warp * 16) / RH < ntok;
+    const int warp_max_pos = pos0 + min(ntok - 1, (warp * 16 + 15) / RH), warp_min_pos = pos0 + (warp * 16) / RH;
+    float O[2 * DV16MAX][4];
+#pragma unroll
+    for (int n = 0; n < 2 * DV16MAX; n++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) O[n][e] = 0.f;
+    if (k_lo < k_hi) {
+        const int* pt = page_table + (long)slot[tok0] * max_pages;
+        const long cw = (long)G * (d + dv);
+        const int kc = d >> 3, vc = dv >> 3;      // 16-byte chunks per row
+        for (int i = tid; i < kMmaRows * kc; i += blockDim.x) {
+            const int r = i / kc, c = i - r * kc, tk = r / RH;
+            const bool ok = tk < ntok;
+            cp_async16(Qs + r * ldk + c * 8, ok ? q + ((long)(tok0 + tk) * H + h0 + r % RH) * d + c * 8 : q, ok);
+        }
+        auto load_tile = [&](int stage, int j0) {
+            __nv_bfloat16* kd = Ks + stage * kMmaKeys * ldk;
+            __nv_bfloat16* vd = Vs + stage * kMmaKeys * ldv;
+            for (int i = tid; i < kMmaKeys * (kc + vc); i += blockDim.x) {
+                const int r = i / (kc + vc), c = i - r * (kc + vc), kp = j0 + r;
+                const bool ok = kp < k_hi;
+                const __nv_bfloat16* src = cache;
+                if (ok) src = cache + ((long)pt[(kp / page_size) % max_pages] * page_size + kp % page_size) * cw + (c < kc ? (long)g * d + c * 8 : (long)G * d + (long)g * dv + (c - kc) * 8);
+                cp_async16(c < kc ? kd + r * ldk + c * 8 : vd + r * ldv + (c - kc) * 8, src, ok);
+            }
+        };
+        load_tile(0, k_lo);
+        const float* bA = biasT + (long)hA * n_bias;
+        const float* bB = biasT + (long)hB * n_bias;
+        const float pbA = pb[hA], pbB = pb[hB];
+        const float farA = bA[n_bias - 1] + pbA, farB = bB[n_bias - 1] + pbB;
+        int stage = 0;
+        for (int j0 = k_lo; j0 < k_hi; j0 += kMmaKeys, stage ^= 1) {
+            cp_async_wait_all();
+            __syncthreads();      // this tile has landed, and every warp is done with the other stage
+            if (j0 + kMmaKeys < k_hi) load_tile(stage ^ 1, j0 + kMmaKeys);
+            if (!warp_live || j0 > warp_max_pos) continue;
+            const __nv_bfloat16* kt = Ks + stage * kMmaKeys * ldk;
+            const __nv_bfloat16* vt = Vs + stage * kMmaKeys * ldv;
+            float S[8][4];
+#pragma unroll
+            for (int n = 0; n < 8; n++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) S[n][e] = 0.f;
+#pragma unroll
+            for (int kk = 0; kk < D16MAX; kk++) {
+                if (kk < d16) {
+                    uint32_t a[4];
+                    ldmatrix_x4(a, Qs + (warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * ldk + kk * 16 + 8 * (lane >> 4));
+#pragma unroll
+                    for (int np = 0; np < 4; np++) {      // two key n-tiles per ldmatrix
+                        uint32_t b[4];
+                        ldmatrix_x4(b, kt + (np * 16 + (lane & 7) + 8 * (lane >> 4)) * ldk + kk * 16 + 8 * ((lane >> 3) & 1));
+                        mma_bf16_16816(S[2 * np], a, b[0], b[1]);
+                        mma_bf16_16816(S[2 * np + 1], a, b[2], b[3]);
+                    }
+                }
+            }
+            const bool far = warp_min_pos - (j0 + kMmaKeys - 1) >= n_bias - 1;      // every distance of this warp's rows in this tile reads the table's last entry
+#pragma unroll
+            for (int n = 0; n < 8; n++) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int key = j0 + n * 8 + 2 * tq + (e & 1);
+                    const bool second = e >= 2;
+                    const int dist = (second ? pB : pA) - key;
+                    const bool ok = (second ? vB : vA) && dist >= 0 && key < k_hi;
+                    float bias_v = second ? farB : farA;
+                    if (!far && ok) bias_v = __ldg((second ? bB : bA) + min(dist, n_bias - 1)) + (second ? pbB : pbA);
+                    S[n][e] = ok ? sigmoid_fast(fmaf(S[n][e], scale, bias_v)) : 0.f;
+                }
+            }
+#pragma unroll
+            for (int kk = 0; kk < 4; kk++) {      // 16 keys per step
+                uint32_t a[4] = {pack_bf16(S[2 * kk][0], S[2 * kk][1]), pack_bf16(S[2 * kk][2], S[2 * kk][3]), pack_bf16(S[2 * kk + 1][0], S[2 * kk + 1][1]),
+                                 pack_bf16(S[2 * kk + 1][2], S[2 * kk + 1][3])};
+#pragma unroll
+                for (int vp = 0; vp < DV16MAX; vp++) {
+                    if (vp < dv16) {
+                        uint32_t b[4];
+                        ldmatrix_x4_trans(b, vt + (kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * ldv + vp * 16 + 8 * (lane >> 4));
+                        mma_bf16_16816(O[2 * vp], a, b[0], b[1]);
+                        mma_bf16_16816(O[2 * vp + 1], a, b[2], b[3]);
+                    }
+                }
+            }
+        }
+        cp_async_wait_all();
+    }
+    const float gA = (vA && !partial) ? sigmoid_f(__bfloat162float(gate[(long)(tok0 + tokA) * gate_stride + hA])) : 0.f;
+    const float gB = (vB && !partial) ? sigmoid_f(__bfloat162float(gate[(long)(tok0 + tokB) * gate_stride + hB])) : 0.f;
+#pragma unroll
+    for (int n = 0; n < 2 * DV16MAX; n++) {
+        const int col = n * 8 + 2 * tq;
+        if (col < dv) {
+            if (partial) {
+                if (vA) *reinterpret_cast<float2*>(partial + (((long)blockIdx.z * n_tokens + tok0 + tokA) * H + hA) * dv + col) = make_float2(O[n][0], O[n][1]);
+                if (vB) *reinterpret_cast<float2*>(partial + (((long)blockIdx.z * n_tokens + tok0 + tokB) * H + hB) * dv + col) = make_float2(O[n][2], O[n][3]);
+            } else {
+                if (vA) *reinterpret_cast<uint32_t*>(out + ((long)(tok0 + tokA) * H + hA) * dv + col) = pack_bf16(O[n][0] * gA, O[n][1] * gA);
+                if (vB) *reinterpret_cast<uint32_t*>(out + ((long)(tok0 + tokB) * H + hB) * dv + col) = pack_bf16(O[n][2] * gB, O[n][3] * gB);
+            }
+        }
     }
 }
 
@@ -362,15 +545,52 @@ extern "C" size_t ktb200_sigmoid_bias_attn_workspace(int n_tokens, int heads, in
     return splits > 1 ? (size_t)splits * n_tokens * heads * vdim * sizeof(float) : 0;
 }
 
+// rows of query heads per tile of the tensor-core kernel: the whole group when it fits 16 rows, else its largest divisor that does
+static int mma_heads_per_tile(int group) {
+    for (int r = group < 16 ? group : 16; r > 1; r--)
+        if (group % r == 0) return r;
+    return 1;
+}
+extern "C" int ktb200_sigmoid_bias_attn_uses_tensor_cores(int heads, int kv_heads, int dim, int vdim, int dtype) {
+    return dtype == KTB200_TYPE_BF16 && kv_heads > 0 && heads % kv_heads == 0 && dim % 16 == 0 && vdim % 16 == 0 && dim <= 128 && vdim <= 128;
+}
+extern "C" int ktb200_sigmoid_bias_attn_tiles(int heads, int kv_heads, int n_tokens, int n_seqs) {
+    return n_seqs + n_tokens / (kMmaRows / mma_heads_per_tile(heads / kv_heads));
+}
+
 extern "C" int ktb200_sigmoid_bias_attn(const void* q, int heads, int kv_heads, int dim, int vdim, float scale, const float* bias, int n_bias, const float* head_bias,
-                                        const int* pos, const int* slot, const int* page_table, int max_pages, int page_size, const void* cache, const void* gate,
-                                        long gate_stride, void* out, int n_tokens, int splits, float* workspace, int dtype, void* stream) {
+                                        const int* pos, const int* slot, const int* seqs, int seqs_stride, int n_seqs, const int* page_table, int max_pages, int page_size,
+                                        const void* cache, const void* gate, long gate_stride, void* out, int n_tokens, int splits, float* workspace, int dtype,
+                                        int allow_tensor_cores, void* stream) {
     if (!q || !bias || !head_bias || !pos || !slot || !page_table || !cache || !gate || !out || heads <= 0 || kv_heads <= 0 || heads % kv_heads || dim <= 0 || vdim <= 0 ||
         vdim > 32 * kAttnMaxCols || n_bias <= 0 || splits < 1 || (splits > 1 && !workspace)) {
         set_error("sigmoid_bias_attn: bad argument");
         return KTB200_EINVAL;
     }
     if (n_tokens <= 0) return KTB200_OK;
+    if (allow_tensor_cores && seqs && n_seqs > 0 && ktb200_sigmoid_bias_attn_uses_tensor_cores(heads, kv_heads, dim, vdim, dtype)) {
+        const int RH = mma_heads_per_tile(heads / kv_heads);
+        const dim3 grid(ktb200_sigmoid_bias_attn_tiles(heads, kv_heads, n_tokens, n_seqs), kv_heads * (heads / kv_heads / RH), splits);
+        const size_t smem = ((size_t)3 * kMmaRows * (dim + kMmaPad) + (size_t)2 * kMmaKeys * (vdim + kMmaPad)) * sizeof(__nv_bfloat16);
+        using B = __nv_bfloat16;
+#define MMA_LAUNCH(DK, DV)                                                                                                                                         \
+    do {                                                                                                                                                           \
+        GRANT_SMEM((sigmoid_attn_mma_kernel<DK, DV>), smem);                                                                                                       \
+        sigmoid_attn_mma_kernel<DK, DV><<<grid, 128, smem, (cudaStream_t)stream>>>((const B*)q, heads, kv_heads, dim, vdim, scale, bias, n_bias, head_bias, pos, slot, seqs,   \
+                                                                                   seqs_stride, n_seqs, RH, page_table, max_pages, page_size, (const B*)cache, (const B*)gate, \
+                                                                                   gate_stride, (B*)out, splits > 1 ? workspace : nullptr, n_tokens);                        \
+    } while (0)
+        if (dim <= 64 && vdim <= 64) MMA_LAUNCH(4, 4);
+        else MMA_LAUNCH(8, 8);
+#undef MMA_LAUNCH
+        KTB_LAUNCH_CHECK();
+        if (splits > 1) {
+            sigmoid_attn_merge_kernel<B><<<grid_for((long)n_tokens * heads * vdim, 256), 256, 0, (cudaStream_t)stream>>>(workspace, splits, (const B*)gate, gate_stride, (B*)out,
+                                                                                                                       n_tokens, heads, vdim);
+            KTB_LAUNCH_CHECK();
+        }
+        return KTB200_OK;
+    }
     const int R = heads / kv_heads, HB = R < 8 ? R : 8, hblocks = (R + HB - 1) / HB;
     const size_t smem = ((size_t)HB * dim + (size_t)kAttnTile * (dim + 1) + (size_t)kAttnTile * vdim + (size_t)HB * n_bias) * sizeof(float);
     if (smem > 200 * 1024) { set_error("sigmoid_bias_attn: head too wide for shared memory"); return KTB200_EINVAL; }

@@ -191,8 +191,8 @@ class KLatentWindowAttention(torch.nn.Module):
 
 
 def distance_bias_table(rel: torch.Tensor, bias_max: float) -> torch.Tensor:
-    """A learned bias per (distance bucket, head), expanded to one row per DISTANCE: rows 0 .. n - 1 with n - 1 the first
-    distance whose bucket is the last one, so a kernel indexes `min(i - j, n - 1)`.  With B rows in `rel` and half = B // 2:
+    """A learned bias per (distance bucket, head), expanded to one entry per DISTANCE and laid out per head, [heads, n]: entries
+    0 .. n - 1 with n - 1 the first distance whose bucket is the last one, so a kernel indexes `[h][min(i - j, n - 1)]`.  With B rows in `rel` and half = B // 2:
     bucket(n) = n below half, else min(B - 1, half + floor(ln(n / half) / ln(bias_max / half) * (B - half))) — exact below half,
     logarithmic up to `bias_max`, constant beyond."""
     B = rel.shape[0]
@@ -204,7 +204,7 @@ def distance_bias_table(rel: torch.Tensor, bias_max: float) -> torch.Tensor:
         if b == B - 1 and n >= half:
             break
         n += 1
-    return rel.float().index_select(0, torch.tensor(buckets, dtype=torch.int64, device=rel.device)).contiguous()
+    return rel.float().index_select(0, torch.tensor(buckets, dtype=torch.int64, device=rel.device)).t().contiguous()
 
 
 class KSigmoidBiasAttention(torch.nn.Module):
@@ -219,6 +219,10 @@ class KSigmoidBiasAttention(torch.nn.Module):
         q, k  -> norms, temperature; [k | v] -> paged cache    ktb200_qk_norm_cache_write
         o_h   = sum_j weight_ij v_j * sigmoid(g_h)             ktb200_sigmoid_bias_attn (fp32 scores and weights)
         out   = W_o o + b_o                                    GEMM
+
+    Two attention kernels (csrc/seq_mixers.cu): in bf16 with head sizes that are multiples of 16 up to 128, tiles of 64 (token,
+    head) rows against 64 keys on the tensor cores (the weights leave the fp32 sigmoid as bf16 operands of the second
+    product); any other size, and fp32, on CUDA cores with fp32 products throughout.
 
     Sizes, scale, the bias table's reach and the temperature constants are constructor parameters
     (models/configuration_mabidra.SigmoidAttentionSpec).  `cache_idx` picks the cache layer, so one set of weights can run
@@ -237,7 +241,7 @@ class KSigmoidBiasAttention(torch.nn.Module):
         self.q_norm, self.k_norm = P(s.dim), P(s.dim)
         self.head_bias = P(s.heads, dt=torch.float32)
         self.o, self.o_b = P(width, s.heads * s.vdim), P(width)
-        self.register_buffer("bias_table", torch.zeros((1, s.heads), dtype=torch.float32, device=device), persistent=False)
+        self.register_buffer("bias_table", torch.zeros((s.heads, 1), dtype=torch.float32, device=device), persistent=False)
 
     def load(self, loader, prefix: str):
         s, t = self.spec, lambda n: loader.load_tensor(prefix + n, "cpu")
@@ -251,10 +255,15 @@ class KSigmoidBiasAttention(torch.nn.Module):
         self.o_b.data.copy_(t("o.b"))
         self.bias_table = distance_bias_table(t("rel"), s.bias_max).to(self.w_in.device)
 
-    def pick_splits(self, n_tokens: int, max_kv: int) -> int:
+    use_tensor_cores = True
+
+    def pick_splits(self, n_tokens: int, max_kv: int, n_seqs: int = 0, tensor_cores: bool = False) -> int:
         """Cut the key range when a small batch would leave most SMs idle on a long context."""
         s = self.spec
-        ctas = n_tokens * s.kv_heads * ((s.heads // s.kv_heads + 7) // 8)
+        if tensor_cores:
+            ctas = native.seq_lib().ktb200_sigmoid_bias_attn_tiles(s.heads, s.kv_heads, n_tokens, n_seqs) * s.kv_heads
+        else:
+            ctas = n_tokens * s.kv_heads * ((s.heads // s.kv_heads + 7) // 8)
         if ctas >= 148 or max_kv <= 256:
             return 1
         return max(1, min(64, max_kv // 128, 592 // ctas))
@@ -270,10 +279,12 @@ class KSigmoidBiasAttention(torch.nn.Module):
                                                         cache.page_table.data_ptr(), cache.max_pages_per_seq, cache.page_size, kv.data_ptr(), q.data_ptr(), T, code, st))
         gate = proj[:, self.n_q + self.n_kv:]
         o = torch.empty((T, s.heads * s.vdim), dtype=dt, device=dev)
-        splits = self.pick_splits(T, batch.max_kv)
+        tc = bool(self.use_tensor_cores and batch.seqs is not None and lib.ktb200_sigmoid_bias_attn_uses_tensor_cores(s.heads, s.kv_heads, s.dim, s.vdim, code))
+        splits = self.pick_splits(T, batch.max_kv, batch.n_seqs, tc)
         ws = torch.empty(lib.ktb200_sigmoid_bias_attn_workspace(T, s.heads, s.vdim, splits) // 4, dtype=torch.float32, device=dev) if splits > 1 else None
-        native.check_seq(lib.ktb200_sigmoid_bias_attn(q.data_ptr(), s.heads, s.kv_heads, s.dim, s.vdim, float(s.scale), self.bias_table.data_ptr(), self.bias_table.shape[0],
-                                                      self.head_bias.data_ptr(), batch.pos.data_ptr(), batch.slot.data_ptr(), cache.page_table.data_ptr(),
-                                                      cache.max_pages_per_seq, cache.page_size, kv.data_ptr(), gate.data_ptr(), self.n_in, o.data_ptr(), T, splits,
-                                                      ws.data_ptr() if ws is not None else None, code, st))
+        native.check_seq(lib.ktb200_sigmoid_bias_attn(q.data_ptr(), s.heads, s.kv_heads, s.dim, s.vdim, float(s.scale), self.bias_table.data_ptr(), self.bias_table.shape[1],
+                                                      self.head_bias.data_ptr(), batch.pos.data_ptr(), batch.slot.data_ptr(),
+                                                      batch.seqs.data_ptr() if tc else None, batch.seqs.stride(0) if tc else 0, batch.n_seqs if tc else 0,
+                                                      cache.page_table.data_ptr(), cache.max_pages_per_seq, cache.page_size, kv.data_ptr(), gate.data_ptr(), self.n_in,
+                                                      o.data_ptr(), T, splits, ws.data_ptr() if ws is not None else None, code, int(tc), st))
         return torch.nn.functional.linear(o, self.o, self.o_b)

@@ -1,5 +1,5 @@
 """Throughput and per-kernel rooflines of a step-function model at layer sizes of real models, with random weights, beside
-the closest existing model's kernels at equal size (`bench.py --model lekapel`).
+the closest existing model's kernels at equal size (`bench.py --model lekapel`, `bench.py --model mabidra`).
 
 Two parts:
   * end to end through the Engine (scheduler, paged cache, step function): prompt tokens/s for a long prompt cut into portions,
@@ -34,10 +34,41 @@ def make_config(s):
     return {"architecture": "Lekapel", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-5, "groups": 4}, "residual_mult": 0.6, "logit_scale": 1.0, "layers": layers}
 
 
-def random_model(cfg_dict, dtype=torch.bfloat16, device="cuda"):
-    from ..models.configuration_lekapel import LekapelConfig
-    from ..models.modeling_lekapel import LekapelForCausalLM
-    model = LekapelForCausalLM(LekapelConfig.from_dict(cfg_dict), dtype=dtype, device=device)
+MABIDRA_SIZES = {
+    # the same widths, feed-forward sizes and layer-run counts as SIZES; attention and linear-attention layers alternate, and the
+    # span `loop` runs twice (6 layer runs for 5 layers / 3 for 2)
+    "2k-wide": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, gla_heads=16, gla_dim=128, gla_vdim=128, rank=64, dense_ff=8192, experts=32, top=4, ff=1024, vocab=32768,
+                    order="AGAGA", loop=(1, 2, 2), ctx=2048),
+    "v3-layer": dict(width=7168, heads=64, kv_heads=8, dim=128, vdim=128, gla_heads=56, gla_dim=128, gla_vdim=128, rank=128, dense_ff=18432, experts=32, top=8, ff=2048, vocab=32768,
+                     order="AG", loop=(1, 2, 2), ctx=4096),
+}
+
+
+def make_mabidra_config(s):
+    attn = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["vdim"], "scale": s["dim"] ** -0.5, "bias_max": 1024, "q_temp": {"coef": 0.1, "every": 512}}
+    gla = {"heads": s["gla_heads"], "dim": s["gla_dim"], "vdim": s["gla_vdim"], "tau": 16.0}
+    moe = {"kind": "moe", "expert": {"ff": s["ff"]}, "router": {"experts": s["experts"], "top": s["top"]}}
+    layers = [{"type": "attention" if c == "A" else "gla", "mixer": attn if c == "A" else gla, "mlp": {"kind": "dense", "ff": s["dense_ff"]} if i == 0 else moe}
+              for i, c in enumerate(s["order"])]
+    return {"architecture": "Mabidra", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-5, "groups": 4}, "embedding": {"scale": 1.0}, "layers": layers,
+            "loop": {"start": s["loop"][0], "stop": s["loop"][1], "times": s["loop"][2]}}
+
+
+def random_model(cfg_dict, dtype=torch.bfloat16, device="cuda", size=None):
+    if cfg_dict["architecture"] == "Mabidra":
+        from ..models.configuration_mabidra import MabidraConfig
+        from ..models.modeling_mabidra import MabidraForCausalLM
+        from ..operators.attention import distance_bias_table
+        model = MabidraForCausalLM(MabidraConfig.from_dict(cfg_dict), dtype=dtype, device=device)
+        for layer in model.layers:
+            if hasattr(layer.mix, "set_rank"):
+                layer.mix.set_rank(size["rank"])
+            else:
+                layer.mix.bias_table = distance_bias_table(torch.randn(64, layer.mix.spec.heads, device=device), layer.mix.spec.bias_max)
+    else:
+        from ..models.configuration_lekapel import LekapelConfig
+        from ..models.modeling_lekapel import LekapelForCausalLM
+        model = LekapelForCausalLM(LekapelConfig.from_dict(cfg_dict), dtype=dtype, device=device)
     g = torch.Generator(device=device).manual_seed(1)
     for name, p in model.named_parameters():
         if p.dim() == 1:
@@ -74,11 +105,11 @@ def timed(fn, flush, iters=10, warmup=3):
     return statistics.median(ts)
 
 
-def engine_leg(name, size, flush, steps, warmup):
+def engine_leg(name, size, flush, steps, warmup, family="lekapel"):
     from .engine import Engine
-    cfg = make_config(size)
-    model = random_model(cfg)
-    prompt_len, chunk, ctx = 4096, 2048, min(4096, size["window"] * 2)
+    cfg = make_config(size) if family == "lekapel" else make_mabidra_config(size)
+    model = random_model(cfg, size=size)
+    prompt_len, chunk, ctx = 4096, 2048, min(4096, size["window"] * 2) if family == "lekapel" else size["ctx"]
     eng = Engine(model, max_tokens=8 * (ctx + 64) + prompt_len, max_slots=9, max_step_tokens=chunk)
     g = torch.Generator().manual_seed(0)
     tok = lambda n: torch.randint(0, size["vocab"], (n,), generator=g).tolist()
@@ -222,8 +253,148 @@ def kernel_leg(flush, peak_gbs, have_main_lib):
     return rows
 
 
+def mabidra_kernel_leg(flush, peak_gbs, peak_tflops):
+    """The kernels of the Mabidra operators at real layer sizes (bf16), each beside the like kernel of the Lekapel path."""
+    dev, bf = torch.device("cuda"), torch.bfloat16
+    seq = native.seq_lib()
+    S = lambda: torch.cuda.current_stream().cuda_stream  # noqa: E731
+    rows = []
+    g = torch.Generator(device=dev).manual_seed(7)
+    rn = lambda *s, dt=bf: torch.randn(*s, generator=g, device=dev, dtype=torch.float32).to(dt)
+
+    def row(kernel, what, ms, nbytes=None, flops=None, peer=None):
+        r = {"kernel": kernel, "case": what, "us": ms * 1e3}
+        if nbytes is not None:
+            r.update(GBps=nbytes / ms / 1e6, frac_of_measured_hbm=nbytes / ms / 1e6 / peak_gbs)
+        if flops is not None:
+            r.update(TFLOPs=flops / ms / 1e9, frac_of_measured_bf16=flops / ms / 1e9 / peak_tflops)
+        if peer:
+            r["closest"] = peer
+        rows.append(r)
+
+    D = 7168
+    for T in (1, 8, 2048):      # residual sum + two grouped norms  vs  residual sum + grouped norm + token shift
+        x, y, w1, w2 = rn(T, D, dt=torch.float32), rn(T, D), rn(D), rn(D)
+        xo, h = torch.empty_like(x), torch.empty(T, D, dtype=bf, device=dev)
+        ours = timed(lambda: native.check_seq(seq.ktb200_group_rmsnorm_sandwich(x.data_ptr(), y.data_ptr(), 30, w1.data_ptr(), None, xo.data_ptr(), w2.data_ptr(), h.data_ptr(), 4,
+                                                                                1e-5, T, D, 30, S())), flush)
+        a, b, mu, hs = rn(T, D), rn(T, D), rn(D), torch.empty(T, D, dtype=bf, device=dev)
+        meta = torch.tensor([[-1] + list(range(T - 1)), [-1] * T, [-1] * (T - 1) + [0]], dtype=torch.int32, device=dev)
+        st = torch.zeros(2, D, device=dev)
+        ms = timed(lambda: native.check_seq(seq.ktb200_group_rmsnorm_shift(x.data_ptr(), a.data_ptr(), 30, b.data_ptr(), 30, 0.6, xo.data_ptr(), w1.data_ptr(), 4, 1e-5, mu.data_ptr(),
+                                                                           meta[0].data_ptr(), meta[1].data_ptr(), meta[2].data_ptr(), st.data_ptr(), h.data_ptr(), hs.data_ptr(), T, D, 30,
+                                                                           S())), flush)
+        pb = T * D * (4 + 2 + 2 + 4 + 2 + 2)
+        row("sandwich_norm_kernel", f"T={T} width={D}", ours, nbytes=T * D * (4 + 2 + 4 + 2),
+            peer={"kernel": "group_norm_shift_kernel", "us": ms * 1e3, "frac_of_measured_hbm": pb / ms / 1e6 / peak_gbs})
+
+    # ---- attention over the paged cache: 64 query heads on 8 key/value heads of 128 + 128 values; the Lekapel kernel beside it reads
+    #      one latent row of 512 + 64 values per key for 128 heads (its tcgen05 path), the same bytes per key within 2x
+    H, G, d, dv, PAGE = 64, 8, 128, 128, 64
+    cw = G * (d + dv)
+    bias, hb = rn(H, 1026, dt=torch.float32), rn(H, dt=torch.float32)
+
+    def lekapel_attn(B, ctx, pos, slot, ptab, pages, T):
+        R, ROPE, NH = 512, 64, 128
+        cache = rn(B * pages + 1, PAGE, R + ROPE)
+        q_abs, q_rot, lat = rn(T, NH, R), rn(T, NH, ROPE), torch.empty(T, NH, R, dtype=bf, device=dev)
+        sink = torch.zeros(NH, device=dev)
+        wsb = seq.ktb200_latent_window_attn_tc_workspace(T, NH, ctx, ctx)
+        tws = torch.empty(wsb // 4, device=dev)
+        return lambda: native.check_seq(seq.ktb200_latent_window_attn_tc(q_abs.data_ptr(), q_rot.data_ptr(), NH, 0.07, sink.data_ptr(), ctx, pos.data_ptr(), slot.data_ptr(),
+                                                                         ptab.data_ptr(), pages, PAGE, cache.data_ptr(), (B * pages + 1) * PAGE, lat.data_ptr(), T, ctx, tws.data_ptr(),
+                                                                         wsb, S()))
+
+    from ..operators.attention import KSigmoidBiasAttention
+    from ..models.configuration_mabidra import SigmoidAttentionSpec
+    spec = SigmoidAttentionSpec(H, G, d, dv, d ** -0.5, 1024.0, 0.1, 512)
+    picker = KSigmoidBiasAttention.pick_splits
+    for B, ctx in ((1, 4096), (8, 4096), (1, 32768)):
+        pages = (ctx + PAGE - 1) // PAGE
+        cache = rn(B * pages + 1, PAGE, cw)
+        ptab = torch.arange(B * pages, dtype=torch.int32, device=dev).reshape(B, pages)
+        q, gate, out = rn(B, H, d), rn(B, H), torch.empty(B, H * dv, dtype=bf, device=dev)
+        pos = torch.full((B,), ctx - 1, dtype=torch.int32, device=dev)
+        slot = torch.arange(B, dtype=torch.int32, device=dev)
+        holder = type("X", (), {"spec": spec})()
+        seqs = torch.tensor([list(range(B)), [1] * B, [-1] * B, [-1] * B], dtype=torch.int32, device=dev)
+        ours = {}
+        for tc in (1, 0):
+            splits = picker(holder, B, ctx, B, bool(tc))
+            ws = torch.empty(max(1, seq.ktb200_sigmoid_bias_attn_workspace(B, H, dv, splits) // 4), device=dev)
+            fn = lambda: native.check_seq(seq.ktb200_sigmoid_bias_attn(q.data_ptr(), H, G, d, dv, d ** -0.5, bias.data_ptr(), bias.shape[1], hb.data_ptr(), pos.data_ptr(), slot.data_ptr(),
+                                                                       seqs.data_ptr(), B, B, ptab.data_ptr(), pages, PAGE, cache.data_ptr(), gate.data_ptr(), H, out.data_ptr(), B, splits,
+                                                                       ws.data_ptr(), 30, tc, S()))
+            ours[tc] = (timed(fn, flush), splits)
+        ms = timed(lekapel_attn(B, ctx, pos, slot, ptab, pages, B), flush)
+        lb = B * ctx * 576 * 2
+        peer = {"kernel": "mla_decode_tc_kernel<split P> (+merge)", "case": "128 heads, latent 512 + 64", "us": ms * 1e3, "frac_of_measured_hbm": lb / ms / 1e6 / peak_gbs}
+        row("sigmoid_attn_mma_kernel (+merge)", f"decode B={B} ctx={ctx} heads={H}/{G} splits={ours[1][1]}", ours[1][0], nbytes=B * ctx * cw * 2, peer=peer)
+        row("sigmoid_attn_kernel (+merge), CUDA cores", f"decode B={B} ctx={ctx} heads={H}/{G} splits={ours[0][1]}", ours[0][0], nbytes=B * ctx * cw * 2, peer=peer)
+    T, ctx = 2048, 4096
+    pages = ctx // PAGE
+    cache = rn(pages + 1, PAGE, cw)
+    ptab = torch.arange(pages, dtype=torch.int32, device=dev).reshape(1, pages)
+    q, gate, out = rn(T, H, d), rn(T, H), torch.empty(T, H * dv, dtype=bf, device=dev)
+    pos = torch.arange(ctx - T, ctx, dtype=torch.int32, device=dev)
+    slot = torch.zeros(T, dtype=torch.int32, device=dev)
+    keys = float(sum(range(ctx - T + 1, ctx + 1)))
+    seqs = torch.tensor([[0], [T], [-1], [-1]], dtype=torch.int32, device=dev)
+    fn = lambda tc: native.check_seq(seq.ktb200_sigmoid_bias_attn(q.data_ptr(), H, G, d, dv, d ** -0.5, bias.data_ptr(), bias.shape[1], hb.data_ptr(), pos.data_ptr(), slot.data_ptr(),
+                                                                  seqs.data_ptr(), 1, 1, ptab.data_ptr(), pages, PAGE, cache.data_ptr(), gate.data_ptr(), H, out.data_ptr(), T, 1, None, 30,
+                                                                  tc, S()))
+    ours = timed(lambda: fn(1), flush, iters=5, warmup=2)
+    slow = timed(lambda: fn(0), flush, iters=2, warmup=1)
+    ms = timed(lekapel_attn(1, ctx, pos, slot, ptab, pages, T), flush, iters=3, warmup=1)
+    lf = keys * 128 * (576 + 512) * 2
+    row("sigmoid_attn_kernel, CUDA cores", f"prompt portion T={T} positions {ctx - T}..{ctx - 1} heads={H}/{G}", slow, flops=keys * H * (d + dv) * 2)
+    row("sigmoid_attn_mma_kernel", f"prompt portion T={T} positions {ctx - T}..{ctx - 1} heads={H}/{G}", ours, flops=keys * H * (d + dv) * 2,
+        peer={"kernel": "mla_decode_tc_kernel<split P>", "case": "128 heads, latent 512 + 64", "us": ms * 1e3, "TFLOPs": lf / ms / 1e9, "frac_of_measured_bf16": lf / ms / 1e9 / peak_tflops})
+
+    # ---- gated linear attention: decode reads and writes the fp32 state once (bytes); a prompt portion is a chain of T dependent steps
+    GH, gd, gdv = 56, 128, 128
+    n_in = 2 * GH * gd + 2 * GH * gdv
+    for B, T in ((1, 1), (8, 1), (1, 2048)):
+        proj, z, zb = rn(B * T, n_in), rn(B * T, GH * gd), rn(GH * gd)
+        state, o = torch.zeros(2 * B, GH * gd * gdv, device=dev), torch.empty(B * T, GH * gdv, device=dev)
+        seqs = torch.tensor([[i * T for i in range(B)], [T] * B, [2 * i for i in range(B)], [2 * i + 1 for i in range(B)]], dtype=torch.int32, device=dev)
+        fn = lambda: native.check_seq(seq.ktb200_gla_scan(proj.data_ptr(), n_in, 0, GH * gd, 2 * GH * gd, z.data_ptr(), GH * gd, zb.data_ptr(), 16.0, GH, gd, gdv, seqs.data_ptr(), B, B,
+                                                          state.data_ptr(), o.data_ptr(), 30, S()))
+        ms = timed(fn, flush, iters=5 if T > 1 else 10)
+        if T == 1:
+            row("gla_scan_kernel", f"decode B={B} heads={GH} dim={gd} vdim={gdv}", ms, nbytes=B * GH * gd * gdv * 8,
+                peer={"note": "no recurrent mixer in the Lekapel path; its decode attention reads the cache rows once, as this reads the state once"})
+        else:
+            row("gla_scan_kernel", f"prompt portion T={T} heads={GH} dim={gd} vdim={gdv}", ms, flops=float(T) * GH * gd * gdv * 4,
+                peer={"note": "fp32 CUDA-core recurrence (state and decays are fp32 by design): %.2f us per token step" % (ms * 1e3 / T)})
+        og, gt, nw = torch.empty(B * T, GH * gdv, dtype=bf, device=dev), rn(B * T, GH * gdv), rn(gdv)
+        ms = timed(lambda: native.check_seq(seq.ktb200_gla_out(o.data_ptr(), nw.data_ptr(), 1e-5, gt.data_ptr(), GH * gdv, og.data_ptr(), B * T, GH, gdv, 30, S())), flush)
+        row("gla_out_kernel", f"T={B * T} heads={GH} vdim={gdv}", ms, nbytes=B * T * GH * gdv * (4 + 2 + 2))
+    # ---- activation
+    for T, ff in ((8, 18432), (2048, 18432)):
+        zz, oo, pq, cf = rn(T, ff), torch.empty(T, ff, dtype=bf, device=dev), torch.tensor([0.3, -0.2], device=dev), torch.tensor([0.3, -0.2, 0.1, 0.0], device=dev)
+        ours = timed(lambda: native.check_seq(seq.ktb200_xielu(zz.data_ptr(), oo.data_ptr(), pq.data_ptr(), zz.numel(), 30, S())), flush)
+        ms = timed(lambda: native.check_seq(seq.ktb200_poly_norm(zz.data_ptr(), oo.data_ptr(), cf.data_ptr(), 1e-5, T, ff, 30, S())), flush)
+        row("xielu_kernel", f"T={T} ff={ff}", ours, nbytes=T * ff * 4, peer={"kernel": "poly_norm_kernel", "us": ms * 1e3, "frac_of_measured_hbm": T * ff * 4 / ms / 1e6 / peak_gbs})
+    # ---- experts without a gate matrix, by expert, beside the gated ones (same kernels, two thirds of the bytes)
+    E, top, ff = 32, 8, 2048
+    Wg, Wu, Wd = rn(E, ff, D), rn(E, ff, D), rn(E, D, ff)
+    for T in (1, 8, 16):
+        x = rn(T, D)
+        ids = torch.stack([torch.randperm(E, generator=g, device=dev)[:top] for _ in range(T)]).to(torch.int64)
+        act = torch.empty(T * top, ff, dtype=bf, device=dev)
+        uniq = len(set(ids.flatten().tolist()))
+        ours = timed(lambda: native.check_seq(seq.ktb200_experts_gate_up_by_expert(x.data_ptr(), ids.data_ptr(), top, E, None, Wu.data_ptr(), act.data_ptr(), T, D, ff, 0, 30, S())), flush)
+        ms = timed(lambda: native.check_seq(seq.ktb200_experts_gate_up_by_expert(x.data_ptr(), ids.data_ptr(), top, E, Wg.data_ptr(), Wu.data_ptr(), act.data_ptr(), T, D, ff, 0, 30, S())), flush)
+        row("experts_gate_up_by_expert_kernel (no gate, relu^2)", f"T={T} top={top} width={D} ff={ff} bf16", ours, nbytes=uniq * ff * D * 2,
+            peer={"kernel": "experts_gate_up_by_expert_kernel (gated)", "us": ms * 1e3, "frac_of_measured_hbm": uniq * 2 * ff * D * 2 / ms / 1e6 / peak_gbs})
+    return rows
+
+
 def run(args):
-    """`bench.py --model lekapel`: prints one JSON line."""
+    """`bench.py --model lekapel | mabidra`: prints one JSON line."""
+    if args.model == "mabidra":
+        return run_mabidra(args)
     torch.cuda.set_device(0)
     root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     try:
@@ -237,6 +408,28 @@ def run(args):
            "timing": "CUDA events, median, 256 MB L2 flush between timed calls", "kernels": kernel_leg(flush, peak, have_main), "models": []}
     for name in (args.sizes.split(",") if getattr(args, "sizes", None) else SIZES):
         out["models"].append(engine_leg(name, SIZES[name], flush, args.steps, args.warmup))
+        torch.cuda.empty_cache()
+    out["gpu_launches"] = int(native.seq_lib().ktb200_launch_count() - n0)
+    print(json.dumps(out))
+
+
+def run_mabidra(args):
+    torch.cuda.set_device(0)
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    try:
+        m = json.load(open(os.path.join(root, "MEASURED_PEAKS.json")))
+        peak, tf, src = float(m["hbm_gbs"]), float(m["bf16_tflops"]), "measured (MEASURED_PEAKS.json hbm_gbs, bf16_tflops)"
+    except Exception:
+        peak, tf, src = 6650.0, 1590.0, "fallback"
+    flush = Flusher("cuda")
+    n0 = native.seq_lib().ktb200_launch_count()
+    out = {"bench": "mabidra", "dtype": "bf16", "data": "synthetic (random weights and tokens)", "hbm_peak_GBps": peak, "bf16_peak_TFLOPs": tf, "peak_source": src,
+           "timing": "CUDA events, median, 256 MB L2 flush between timed calls", "kernels": [] if getattr(args, "no_kernels", False) else mabidra_kernel_leg(flush, peak, tf),
+           "models": [], "closest_models": []}
+    for name in (args.sizes.split(",") if getattr(args, "sizes", None) else MABIDRA_SIZES):
+        out["models"].append(engine_leg(name, MABIDRA_SIZES[name], flush, args.steps, args.warmup, family="mabidra"))
+        torch.cuda.empty_cache()
+        out["closest_models"].append(engine_leg(name, SIZES[name], flush, args.steps, args.warmup))      # Lekapel at the same widths, in the same process
         torch.cuda.empty_cache()
     out["gpu_launches"] = int(native.seq_lib().ktb200_launch_count() - n0)
     print(json.dumps(out))

@@ -106,10 +106,10 @@ def test_distance_bias_table_lists_the_bucket_of_every_distance(rows, reach):
     from ktransformers_b200.operators.attention import distance_bias_table
     rel_t = torch.arange(rows * 3, dtype=torch.float32).reshape(rows, 3)
     table = distance_bias_table(rel_t, reach)
-    n = table.shape[0]
-    assert n <= int(reach) + 2 and O.distance_bucket(n - 1, rows, reach) == rows - 1
+    n = table.shape[1]                                           # [heads, distances]
+    assert table.shape[0] == 3 and n <= int(reach) + 2 and O.distance_bucket(n - 1, rows, reach) == rows - 1
     for dist in list(range(n + 5)) + [10 ** 6]:
-        assert torch.equal(table[min(dist, n - 1)], rel_t[O.distance_bucket(dist, rows, reach)])
+        assert torch.equal(table[:, min(dist, n - 1)], rel_t[O.distance_bucket(dist, rows, reach)])
     assert [O.distance_bucket(x, 8, 11) for x in (0, 3, 4, 5, 10, 11, 12)] == [0, 3, 4, 4, 7, 7, 7]
 
 
@@ -211,7 +211,7 @@ def test_topk_softmax_moe_with_relu_squared_experts(dtype, tol, experts, top, ff
     assert rel(op(h.cuda()), O.relu2_moe_mlp(h.double(), Wd, top)) < tol
 
 
-def mixer_alone(desc, dtype, n, page_size, portions, big_at=None, big=30.0, seed=4, width=24, tweak=None):
+def mixer_alone(desc, dtype, n, page_size, portions, big_at=None, big=30.0, seed=4, width=24, tweak=None, tensor_cores=True):
     """one mixer operator over one sequence cut into `portions`, against the restatement over the whole sequence; `big_at`:
     the input row of that token is scaled, so its un-normed value (and key, for the recurrence) stands out"""
     from ktransformers_b200.models.configuration_mabidra import MIXER_SPECS
@@ -225,6 +225,7 @@ def mixer_alone(desc, dtype, n, page_size, portions, big_at=None, big=30.0, seed
     spec = MIXER_SPECS[desc["type"]].from_dict(m)
     op = MIXERS[desc["type"]](width, spec, 1e-5, dtype=dtype)
     op.load(DictLoader(W), "")
+    op.use_tensor_cores = tensor_cores
     g = torch.Generator().manual_seed(seed)
     h = torch.randn(n, width, generator=g)
     if big_at is not None:
@@ -289,6 +290,35 @@ def test_far_value_among_hundreds_and_the_split_path():
         assert rel(got, want) < 2e-5
     got, want = mixer_alone(U.attn(heads=16, kv_heads=2), torch.bfloat16, 600, 64, [590, 2] + [1] * 8, big_at=64)
     assert rel(got, want) < 4e-2
+
+
+MMA_SHAPES = [U.attn(heads=8, kv_heads=2, dim=16, vdim=32), U.attn(heads=9, kv_heads=1, dim=48, vdim=16, rows=32, bias_max=60, every=64),
+              U.attn(heads=34, kv_heads=2, dim=32, vdim=32, rows=6, bias_max=9.5), U.attn(heads=4, kv_heads=4, dim=128, vdim=128, rows=16, bias_max=100, every=50),
+              U.attn(heads=12, kv_heads=1, dim=64, vdim=80, rows=4, bias_max=300), U.attn(heads=40, kv_heads=2, dim=16, vdim=112, rows=8, bias_max=70)]
+
+
+@gpu
+@pytest.mark.parametrize("desc", MMA_SHAPES)
+def test_tensor_core_attention_path(desc):
+    """bf16 with head sizes that are multiples of 16 takes the tensor-core tiles: against the restatement, and against the
+    CUDA-core kernel on the same bf16 inputs (between the two: bf16 weights in the second product, and the order of the sums).
+    200 tokens cross three key tiles; portions start and end inside tiles; the value that stands out sits at a tile's edge"""
+    for portions, at in (([200], 7), ([129, 1, 1, 30, 2, 37], 63), ([64, 64, 8, 1], 64), ([190] + [1] * 10, 127)):
+        got, want = mixer_alone(desc, torch.bfloat16, 200, 16, portions, big_at=at)
+        simple, _ = mixer_alone(desc, torch.bfloat16, 200, 16, portions, big_at=at, tensor_cores=False)
+        assert rel(got, want) < 4e-2 and rel(simple, want) < 4e-2
+        assert rel(got, simple) < 1.5e-2
+        assert rel(got[:3], want[:3]) < 4e-2 and rel(got[at:at + 3], want[at:at + 3]) < 4e-2
+
+
+@gpu
+def test_tensor_core_attention_far_value_and_split_edges():
+    """decode over a long range on the tensor-core path cuts the keys into parts of whole tiles"""
+    desc = U.attn(heads=16, kv_heads=2, dim=32, vdim=48)
+    for at in (3, 127, 128, 383, 384, 640):
+        got, want = mixer_alone(desc, torch.bfloat16, 700, 64, [690] + [1] * 10, big_at=at)
+        simple, _ = mixer_alone(desc, torch.bfloat16, 700, 64, [690] + [1] * 10, big_at=at, tensor_cores=False)
+        assert rel(got, want) < 4e-2 and rel(got[690:], want[690:]) < 4e-2 and rel(got, simple) < 1.5e-2
 
 
 GLA_SHAPES = [U.gla(), U.gla(heads=2, dim=17, vdim=33, tau=9.0, rank=3), U.gla(heads=1, dim=64, vdim=64, tau=16.0, rank=8), U.gla(heads=5, dim=3, vdim=1, tau=1.0, rank=1),
