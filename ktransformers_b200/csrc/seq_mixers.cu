@@ -278,18 +278,23 @@ __global__ void __launch_bounds__(128) sigmoid_attn_mma_kernel(const __nv_bfloat
             const bool ok = tk < ntok;
             cp_async16(Qs + r * ldk + c * 8, ok ? q + ((long)(tok0 + tk) * H + h0 + r % RH) * d + c * 8 : q, ok);
         }
-        auto load_tile = [&](int stage, int j0) {
-            __nv_bfloat16* kd = Ks + stage * kMmaKeys * ldk;
-            __nv_bfloat16* vd = Vs + stage * kMmaKeys * ldv;
-            for (int i = tid; i < kMmaKeys * (kc + vc); i += blockDim.x) {
-                const int r = i / (kc + vc), c = i - r * (kc + vc), kp = j0 + r;
-                const bool ok = kp < k_hi;
-                const __nv_bfloat16* src = cache;
-                if (ok) src = cache + ((long)pt[(kp / page_size) % max_pages] * page_size + kp % page_size) * cw + (c < kc ? (long)g * d + c * 8 : (long)G * d + (long)g * dv + (c - kc) * 8);
-                cp_async16(c < kc ? kd + r * ldk + c * 8 : vd + r * ldv + (c - kc) * 8, src, ok);
-            }
+        // thread pair (2r, 2r + 1) copies key row r of a tile: one page-table lookup per thread and tile, made a tile ahead of its
+        // copies, and 16-byte chunks that alternate between the two threads (a pair fills whole 32-byte sectors)
+        const int lrow = tid >> 1, lpar = tid & 1;
+        auto row_base = [&](int kp) -> long {
+            return kp < k_hi ? ((long)pt[(kp / page_size) % max_pages] * page_size + kp % page_size) * cw : -1;
         };
-        load_tile(0, k_lo);
+        auto load_tile = [&](int stage, long base) {
+            __nv_bfloat16* kd = Ks + stage * kMmaKeys * ldk + lrow * ldk;
+            __nv_bfloat16* vd = Vs + stage * kMmaKeys * ldv + lrow * ldv;
+            const bool ok = base >= 0;
+            const __nv_bfloat16* ksrc = ok ? cache + base + (long)g * d : cache;
+            const __nv_bfloat16* vsrc = ok ? cache + base + (long)G * d + (long)g * dv : cache;
+            for (int c = lpar; c < kc; c += 2) cp_async16(kd + c * 8, ok ? ksrc + c * 8 : cache, ok);
+            for (int c = lpar; c < vc; c += 2) cp_async16(vd + c * 8, ok ? vsrc + c * 8 : cache, ok);
+        };
+        load_tile(0, row_base(k_lo + lrow));
+        long next_base = row_base(k_lo + kMmaKeys + lrow);
         const float* bA = biasT + (long)hA * n_bias;
         const float* bB = biasT + (long)hB * n_bias;
         const float pbA = pb[hA], pbB = pb[hB];
@@ -298,7 +303,10 @@ __global__ void __launch_bounds__(128) sigmoid_attn_mma_kernel(const __nv_bfloat
         for (int j0 = k_lo; j0 < k_hi; j0 += kMmaKeys, stage ^= 1) {
             cp_async_wait_all();
             __syncthreads();      // this tile has landed, and every warp is done with the other stage
-            if (j0 + kMmaKeys < k_hi) load_tile(stage ^ 1, j0 + kMmaKeys);
+            if (j0 + kMmaKeys < k_hi) {
+                load_tile(stage ^ 1, next_base);
+                next_base = row_base(j0 + 2 * kMmaKeys + lrow);
+            }
             if (!warp_live || j0 > warp_max_pos) continue;
             const __nv_bfloat16* kt = Ks + stage * kMmaKeys * ldk;
             const __nv_bfloat16* vt = Vs + stage * kMmaKeys * ldv;
@@ -383,8 +391,8 @@ __global__ void sigmoid_attn_merge_kernel(const float* __restrict__ partial, int
 }
 
 // ------------------------------------------------------------------------------------------------ gated linear attention
-// grid (sequence portions, heads, column blocks of 32 value columns); 8 warps; thread (warp w, lane) keeps S[i][col] for the
-// key channels i = w + 8 r in registers.  Tokens run in order in chunks of kGlaChunk staged in shared memory; per token every
+// grid (sequence portions, heads, column blocks of 32 value columns); 8 warps; thread (warp w, lane) keeps S[i][col] for a
+// contiguous run of key channels i in registers.  Tokens run in order in chunks of kGlaChunk staged in shared memory; per token every
 // warp leaves its part of o in shared memory, and the parts are summed in warp order once per chunk.  The arithmetic of a token
 // does not depend on where a portion starts or ends.
 constexpr int kGlaChunk = 16;
@@ -395,10 +403,12 @@ __global__ void __launch_bounds__(256) gla_scan_kernel(const T* __restrict__ pro
                                                        const T* __restrict__ z_bias, float inv_tau, float q_scale, int H, int d, int dv, const int* __restrict__ seqs,
                                                        int seqs_stride, float* __restrict__ state, float* __restrict__ o_out) {
     extern __shared__ __align__(16) float sm[];
-    float* qs = sm;                             // [chunk][d]
-    float* ks = qs + kGlaChunk * d;             // [chunk][d]
-    float* as = ks + kGlaChunk * d;             // [chunk][d]
-    float* vs = as + kGlaChunk * d;             // [chunk][32]
+    // warp w owns the key channels w * rpt .. w * rpt + rpt - 1 (rpt a multiple of 4: float4 reads); channels >= d are zero
+    const int rpt = (((d + kGlaWarps - 1) / kGlaWarps) + 3) & ~3, dp = rpt * kGlaWarps;
+    float* qs = sm;                             // [chunk][dp]
+    float* ks = qs + kGlaChunk * dp;            // [chunk][dp]
+    float* as = ks + kGlaChunk * dp;            // [chunk][dp]
+    float* vs = as + kGlaChunk * dp;            // [chunk][32]
     float* part = vs + kGlaChunk * 32;          // [chunk][warps][32]
     const int s = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * 32;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, col = c0 + lane;
@@ -407,18 +417,19 @@ __global__ void __launch_bounds__(256) gla_scan_kernel(const T* __restrict__ pro
     float S[kGlaRows];
 #pragma unroll
     for (int r = 0; r < kGlaRows; r++) {
-        const int i = warp + kGlaWarps * r;
-        S[r] = (rd >= 0 && i < d && col < dv) ? state[rd * srow + ((long)h * d + i) * dv + col] : 0.f;
+        const int i = warp * rpt + r;
+        S[r] = (rd >= 0 && r < rpt && i < d && col < dv) ? state[rd * srow + ((long)h * d + i) * dv + col] : 0.f;
     }
     for (int t0 = 0; t0 < len; t0 += kGlaChunk) {
         const int nt = min(kGlaChunk, len - t0);
         __syncthreads();
-        for (int i = threadIdx.x; i < nt * d; i += blockDim.x) {
-            const int tt = i / d, c = i - tt * d;
+        for (int i = threadIdx.x; i < nt * dp; i += blockDim.x) {
+            const int tt = i / dp, c = i - tt * dp;
             const long row = (long)(start + t0 + tt);
-            qs[i] = to_f(proj[row * proj_stride + q_off + h * d + c]) * q_scale;
-            ks[i] = to_f(proj[row * proj_stride + k_off + h * d + c]);
-            as[i] = expf(log_sigmoid_f(to_f(z[row * z_stride + h * d + c]) + to_f(z_bias[h * d + c])) * inv_tau);
+            const bool in = c < d;
+            qs[i] = in ? to_f(proj[row * proj_stride + q_off + h * d + c]) * q_scale : 0.f;
+            ks[i] = in ? to_f(proj[row * proj_stride + k_off + h * d + c]) : 0.f;
+            as[i] = in ? expf(log_sigmoid_f(to_f(z[row * z_stride + h * d + c]) + to_f(z_bias[h * d + c])) * inv_tau) : 0.f;
         }
         for (int i = threadIdx.x; i < nt * 32; i += blockDim.x) {
             const int tt = i >> 5, c = c0 + (i & 31);
@@ -427,16 +438,22 @@ __global__ void __launch_bounds__(256) gla_scan_kernel(const T* __restrict__ pro
         __syncthreads();
         for (int tt = 0; tt < nt; tt++) {
             const float v = vs[tt * 32 + lane];
-            const float* qr = qs + tt * d;
-            const float* kr = ks + tt * d;
-            const float* ar = as + tt * d;
+            const float4* qr = reinterpret_cast<const float4*>(qs + tt * dp + warp * rpt);
+            const float4* kr = reinterpret_cast<const float4*>(ks + tt * dp + warp * rpt);
+            const float4* ar = reinterpret_cast<const float4*>(as + tt * dp + warp * rpt);
             float po = 0.f;
 #pragma unroll
-            for (int r = 0; r < kGlaRows; r++) {
-                const int i = warp + kGlaWarps * r;
-                if (i < d) {
-                    S[r] = fmaf(ar[i], S[r], kr[i] * v);
-                    po = fmaf(S[r], qr[i], po);
+            for (int r4 = 0; r4 < kGlaRows / 4; r4++) {
+                if (4 * r4 < rpt) {
+                    const float4 a = ar[r4], k = kr[r4], qv = qr[r4];
+                    S[4 * r4] = fmaf(a.x, S[4 * r4], k.x * v);
+                    po = fmaf(S[4 * r4], qv.x, po);
+                    S[4 * r4 + 1] = fmaf(a.y, S[4 * r4 + 1], k.y * v);
+                    po = fmaf(S[4 * r4 + 1], qv.y, po);
+                    S[4 * r4 + 2] = fmaf(a.z, S[4 * r4 + 2], k.z * v);
+                    po = fmaf(S[4 * r4 + 2], qv.z, po);
+                    S[4 * r4 + 3] = fmaf(a.w, S[4 * r4 + 3], k.w * v);
+                    po = fmaf(S[4 * r4 + 3], qv.w, po);
                 }
             }
             part[(tt * kGlaWarps + warp) * 32 + lane] = po;
@@ -453,8 +470,8 @@ __global__ void __launch_bounds__(256) gla_scan_kernel(const T* __restrict__ pro
     if (wr >= 0) {
 #pragma unroll
         for (int r = 0; r < kGlaRows; r++) {
-            const int i = warp + kGlaWarps * r;
-            if (i < d && col < dv) state[wr * srow + ((long)h * d + i) * dv + col] = S[r];
+            const int i = warp * rpt + r;
+            if (r < rpt && i < d && col < dv) state[wr * srow + ((long)h * d + i) * dv + col] = S[r];
         }
     }
 }
@@ -616,7 +633,8 @@ extern "C" int ktb200_gla_scan(const void* proj, long proj_stride, int q_off, in
         return KTB200_EINVAL;
     }
     if (n_seqs <= 0) return KTB200_OK;
-    const size_t smem = ((size_t)3 * kGlaChunk * dim + kGlaChunk * 32 + (size_t)kGlaChunk * kGlaWarps * 32) * sizeof(float);
+    const int dp = ((((dim + kGlaWarps - 1) / kGlaWarps) + 3) & ~3) * kGlaWarps;      // key channels padded to whole float4 per warp
+    const size_t smem = ((size_t)3 * kGlaChunk * dp + kGlaChunk * 32 + (size_t)kGlaChunk * kGlaWarps * 32) * sizeof(float);
     SEQ_DISPATCH(dtype, {
         GRANT_SMEM(gla_scan_kernel<T>, smem);
         gla_scan_kernel<T><<<dim3(n_seqs, heads, (vdim + 31) / 32), kGlaWarps * 32, smem, (cudaStream_t)stream>>>(

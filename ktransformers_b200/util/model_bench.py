@@ -13,6 +13,7 @@ import ctypes as C
 import json
 import os
 import statistics
+import sys
 
 import torch
 
@@ -82,6 +83,10 @@ def model_bytes(model):
     return sum(p.numel() * p.element_size() for p in model.parameters())
 
 
+def progress(msg):
+    print("[model_bench] " + msg, file=sys.stderr, flush=True)
+
+
 class Flusher:
     def __init__(self, dev):
         self.buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
@@ -114,6 +119,7 @@ def engine_leg(name, size, flush, steps, warmup, family="lekapel"):
     g = torch.Generator().manual_seed(0)
     tok = lambda n: torch.randint(0, size["vocab"], (n,), generator=g).tolist()
     out = {"size": name, "config": {k: v for k, v in size.items()}, "weights_GB": model_bytes(model) / 1e9}
+    progress(f"{family} {name}: model built")
 
     def prefill():
         p = tok(prompt_len)
@@ -121,6 +127,7 @@ def engine_leg(name, size, flush, steps, warmup, family="lekapel"):
             eng.step([("p", p[lo:lo + chunk], [len(p[lo:lo + chunk]) - 1] if lo + chunk >= prompt_len else [])], ["p"] if lo + chunk >= prompt_len else [])
     ms = timed(prefill, flush, iters=max(3, steps // 4), warmup=max(1, warmup // 2))
     out["prefill"] = {"prompt_tokens": prompt_len, "portion": chunk, "ms": ms, "tok_s": prompt_len / ms * 1e3}
+    progress(f"{family} {name}: prefill {ms:.1f} ms")
     for bs in (1, 8):
         ids = [("d", i) for i in range(bs)]
         for i in ids:                                     # fill each sequence's cache to ctx tokens
@@ -132,6 +139,7 @@ def engine_leg(name, size, flush, steps, warmup, family="lekapel"):
         for i in ids:
             eng.cache.close(i)
         out[f"decode_bs{bs}"] = {"ctx": ctx, "ms_per_step": ms, "tok_s": bs / ms * 1e3}
+        progress(f"{family} {name}: decode x{bs} {ms:.3f} ms")
     return out
 
 
@@ -264,6 +272,7 @@ def mabidra_kernel_leg(flush, peak_gbs, peak_tflops):
 
     def row(kernel, what, ms, nbytes=None, flops=None, peer=None):
         r = {"kernel": kernel, "case": what, "us": ms * 1e3}
+        progress(f"{kernel} {what}: {ms * 1e3:.1f} us")
         if nbytes is not None:
             r.update(GBps=nbytes / ms / 1e6, frac_of_measured_hbm=nbytes / ms / 1e6 / peak_gbs)
         if flops is not None:
