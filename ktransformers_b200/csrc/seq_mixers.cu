@@ -188,8 +188,8 @@ __global__ void __launch_bounds__(256) sigmoid_attn_kernel(const T* __restrict__
 }
 
 // ------------------------------------------------------------------------------------------------ sigmoid attention, tensor cores (bf16)
-// A CTA of 4 warps owns a tile of 64 rows = (token, query head) pairs of ONE sequence portion and ONE key/value head: `RH` query
-// heads of the group for each of 64 / RH consecutive tokens (prompt portions fill the rows with tokens, decode steps with the
+// A CTA of ROWS / 16 warps owns a tile of ROWS (64 or 128) rows = (token, query head) pairs of ONE sequence portion and ONE key/value
+// head: `RH` query heads of the group for each of ROWS / RH consecutive tokens; KEYS = 64 or 32 keys per ring stage (prompt portions fill the rows with tokens, decode steps with the
 // group's heads).  Keys run in tiles of 64 through a two-stage cp.async ring of [k | v] rows gathered through the page table;
 // S = Q K^T and O += P V are m16n8k16 bf16 MMAs with fp32 accumulators; the scores are scaled, biased and pushed through the
 // sigmoid in fp32 registers and handed to the second product as bf16.  No running maximum and no rescaling: the weights are
@@ -221,8 +221,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 __device__ __forceinline__ float sigmoid_fast(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 
-template <int D16MAX, int DV16MAX>
-__global__ void __launch_bounds__(128) sigmoid_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, int H, int G, int d, int dv, float scale, const float* __restrict__ biasT,
+template <int D16MAX, int DV16MAX, int ROWS, int KEYS>
+__global__ void __launch_bounds__(ROWS * 2, (ROWS == 64 && KEYS == 32) ? 4 : 1) sigmoid_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, int H, int G, int d, int dv, float scale, const float* __restrict__ biasT,
                                                                int n_bias, const float* __restrict__ pb, const int* __restrict__ pos, const int* __restrict__ slot,
                                                                const int* __restrict__ seqs, int seqs_stride, int n_seqs, int RH, const int* __restrict__ page_table,
                                                                int max_pages, int page_size, const __nv_bfloat16* __restrict__ cache,
@@ -231,7 +231,7 @@ __global__ void __launch_bounds__(128) sigmoid_attn_mma_kernel(const __nv_bfloat
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ int tile_info[3];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gq = lane >> 2, tq = lane & 3;
-    const int TOKS = kMmaRows / RH;
+    const int TOKS = ROWS / RH;
     if (tid == 0) {      // which sequence portion and which of its tokens this tile covers
         int b = blockIdx.x, found = -1, off = 0, len = 0;
         for (int s = 0; s < n_seqs; s++) {
@@ -251,8 +251,8 @@ __global__ void __launch_bounds__(128) sigmoid_attn_mma_kernel(const __nv_bfloat
     const int g = blockIdx.y / hblocks, h0 = g * R + (blockIdx.y % hblocks) * RH;
     const int d16 = d >> 4, dv16 = dv >> 4, ldk = d + kMmaPad, ldv = dv + kMmaPad;
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-    __nv_bfloat16* Ks = Qs + kMmaRows * ldk;                 // [2][64][ldk]
-    __nv_bfloat16* Vs = Ks + 2 * kMmaKeys * ldk;             // [2][64][ldv]
+    __nv_bfloat16* Ks = Qs + ROWS * ldk;                 // [2][KEYS][ldk]
+    __nv_bfloat16* Vs = Ks + 2 * KEYS * ldk;                 // [2][KEYS][ldv]
     const int pos0 = pos[tok0], max_pos = pos0 + ntok - 1;
     const int splits = gridDim.z, n_keys = max_pos + 1;
     const int per = ((n_keys + splits - 1) / splits + kMmaKeys - 1) / kMmaKeys * kMmaKeys;
@@ -273,46 +273,47 @@ __global__ void __launch_bounds__(128) sigmoid_attn_mma_kernel(const __nv_bfloat
         const int* pt = page_table + (long)slot[tok0] * max_pages;
         const long cw = (long)G * (d + dv);
         const int kc = d >> 3, vc = dv >> 3;      // 16-byte chunks per row
-        for (int i = tid; i < kMmaRows * kc; i += blockDim.x) {
+        for (int i = tid; i < ROWS * kc; i += blockDim.x) {
             const int r = i / kc, c = i - r * kc, tk = r / RH;
             const bool ok = tk < ntok;
             cp_async16(Qs + r * ldk + c * 8, ok ? q + ((long)(tok0 + tk) * H + h0 + r % RH) * d + c * 8 : q, ok);
         }
-        // thread pair (2r, 2r + 1) copies key row r of a tile: one page-table lookup per thread and tile, made a tile ahead of its
-        // copies, and 16-byte chunks that alternate between the two threads (a pair fills whole 32-byte sectors)
-        const int lrow = tid >> 1, lpar = tid & 1;
+        // TPR = 2 or 4 neighbouring threads copy key row r of a tile: one page-table lookup per thread and tile, made a tile ahead
+        // of its copies, and 16-byte chunks dealt round the TPR threads (together they fill whole 32-byte sectors)
+        constexpr int TPR = ROWS * 2 / KEYS;
+        const int lrow = tid / TPR, lpar = tid % TPR;
         auto row_base = [&](int kp) -> long {
             return kp < k_hi ? ((long)pt[(kp / page_size) % max_pages] * page_size + kp % page_size) * cw : -1;
         };
         auto load_tile = [&](int stage, long base) {
-            __nv_bfloat16* kd = Ks + stage * kMmaKeys * ldk + lrow * ldk;
-            __nv_bfloat16* vd = Vs + stage * kMmaKeys * ldv + lrow * ldv;
+            __nv_bfloat16* kd = Ks + stage * KEYS * ldk + lrow * ldk;
+            __nv_bfloat16* vd = Vs + stage * KEYS * ldv + lrow * ldv;
             const bool ok = base >= 0;
             const __nv_bfloat16* ksrc = ok ? cache + base + (long)g * d : cache;
             const __nv_bfloat16* vsrc = ok ? cache + base + (long)G * d + (long)g * dv : cache;
-            for (int c = lpar; c < kc; c += 2) cp_async16(kd + c * 8, ok ? ksrc + c * 8 : cache, ok);
-            for (int c = lpar; c < vc; c += 2) cp_async16(vd + c * 8, ok ? vsrc + c * 8 : cache, ok);
+            for (int c = lpar; c < kc; c += TPR) cp_async16(kd + c * 8, ok ? ksrc + c * 8 : cache, ok);
+            for (int c = lpar; c < vc; c += TPR) cp_async16(vd + c * 8, ok ? vsrc + c * 8 : cache, ok);
         };
         load_tile(0, row_base(k_lo + lrow));
-        long next_base = row_base(k_lo + kMmaKeys + lrow);
+        long next_base = row_base(k_lo + KEYS + lrow);
         const float* bA = biasT + (long)hA * n_bias;
         const float* bB = biasT + (long)hB * n_bias;
         const float pbA = pb[hA], pbB = pb[hB];
         const float farA = bA[n_bias - 1] + pbA, farB = bB[n_bias - 1] + pbB;
         int stage = 0;
-        for (int j0 = k_lo; j0 < k_hi; j0 += kMmaKeys, stage ^= 1) {
+        for (int j0 = k_lo; j0 < k_hi; j0 += KEYS, stage ^= 1) {
             cp_async_wait_all();
             __syncthreads();      // this tile has landed, and every warp is done with the other stage
-            if (j0 + kMmaKeys < k_hi) {
+            if (j0 + KEYS < k_hi) {
                 load_tile(stage ^ 1, next_base);
-                next_base = row_base(j0 + 2 * kMmaKeys + lrow);
+                next_base = row_base(j0 + 2 * KEYS + lrow);
             }
             if (!warp_live || j0 > warp_max_pos) continue;
-            const __nv_bfloat16* kt = Ks + stage * kMmaKeys * ldk;
-            const __nv_bfloat16* vt = Vs + stage * kMmaKeys * ldv;
-            float S[8][4];
+            const __nv_bfloat16* kt = Ks + stage * KEYS * ldk;
+            const __nv_bfloat16* vt = Vs + stage * KEYS * ldv;
+            float S[KEYS / 8][4];
 #pragma unroll
-            for (int n = 0; n < 8; n++)
+            for (int n = 0; n < KEYS / 8; n++)
 #pragma unroll
                 for (int e = 0; e < 4; e++) S[n][e] = 0.f;
 #pragma unroll
@@ -321,7 +322,7 @@ __global__ void __launch_bounds__(128) sigmoid_attn_mma_kernel(const __nv_bfloat
                     uint32_t a[4];
                     ldmatrix_x4(a, Qs + (warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * ldk + kk * 16 + 8 * (lane >> 4));
 #pragma unroll
-                    for (int np = 0; np < 4; np++) {      // two key n-tiles per ldmatrix
+                    for (int np = 0; np < KEYS / 16; np++) {      // two key n-tiles per ldmatrix
                         uint32_t b[4];
                         ldmatrix_x4(b, kt + (np * 16 + (lane & 7) + 8 * (lane >> 4)) * ldk + kk * 16 + 8 * ((lane >> 3) & 1));
                         mma_bf16_16816(S[2 * np], a, b[0], b[1]);
@@ -329,9 +330,9 @@ __global__ void __launch_bounds__(128) sigmoid_attn_mma_kernel(const __nv_bfloat
                     }
                 }
             }
-            const bool far = warp_min_pos - (j0 + kMmaKeys - 1) >= n_bias - 1;      // every distance of this warp's rows in this tile reads the table's last entry
+            const bool far = warp_min_pos - (j0 + KEYS - 1) >= n_bias - 1;      // every distance of this warp's rows in this tile reads the table's last entry
 #pragma unroll
-            for (int n = 0; n < 8; n++) {
+            for (int n = 0; n < KEYS / 8; n++) {
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
                     const int key = j0 + n * 8 + 2 * tq + (e & 1);
@@ -344,7 +345,7 @@ __global__ void __launch_bounds__(128) sigmoid_attn_mma_kernel(const __nv_bfloat
                 }
             }
 #pragma unroll
-            for (int kk = 0; kk < 4; kk++) {      // 16 keys per step
+            for (int kk = 0; kk < KEYS / 16; kk++) {      // 16 keys per step
                 uint32_t a[4] = {pack_bf16(S[2 * kk][0], S[2 * kk][1]), pack_bf16(S[2 * kk][2], S[2 * kk][3]), pack_bf16(S[2 * kk + 1][0], S[2 * kk + 1][1]),
                                  pack_bf16(S[2 * kk + 1][2], S[2 * kk + 1][3])};
 #pragma unroll
@@ -571,8 +572,12 @@ static int mma_heads_per_tile(int group) {
 extern "C" int ktb200_sigmoid_bias_attn_uses_tensor_cores(int heads, int kv_heads, int dim, int vdim, int dtype) {
     return dtype == KTB200_TYPE_BF16 && kv_heads > 0 && heads % kv_heads == 0 && dim % 16 == 0 && vdim % 16 == 0 && dim <= 128 && vdim <= 128;
 }
+// whether the batch is prompt-sized: the sequence portions bring 128 or more (token, head) rows on average
+static int mma_rows_per_tile(int group, int n_tokens, int n_seqs) {
+    return (long)n_tokens * mma_heads_per_tile(group) >= (long)128 * (n_seqs > 0 ? n_seqs : 1) ? 128 : 64;
+}
 extern "C" int ktb200_sigmoid_bias_attn_tiles(int heads, int kv_heads, int n_tokens, int n_seqs) {
-    return n_seqs + n_tokens / (kMmaRows / mma_heads_per_tile(heads / kv_heads));
+    return n_seqs + n_tokens / (64 / mma_heads_per_tile(heads / kv_heads));
 }
 
 extern "C" int ktb200_sigmoid_bias_attn(const void* q, int heads, int kv_heads, int dim, int vdim, float scale, const float* bias, int n_bias, const float* head_bias,
@@ -586,19 +591,23 @@ extern "C" int ktb200_sigmoid_bias_attn(const void* q, int heads, int kv_heads, 
     }
     if (n_tokens <= 0) return KTB200_OK;
     if (allow_tensor_cores && seqs && n_seqs > 0 && ktb200_sigmoid_bias_attn_uses_tensor_cores(heads, kv_heads, dim, vdim, dtype)) {
-        const int RH = mma_heads_per_tile(heads / kv_heads);
+        const int RH = mma_heads_per_tile(heads / kv_heads), rows = mma_rows_per_tile(heads / kv_heads, n_tokens, n_seqs);
         const dim3 grid(ktb200_sigmoid_bias_attn_tiles(heads, kv_heads, n_tokens, n_seqs), kv_heads * (heads / kv_heads / RH), splits);
-        const size_t smem = ((size_t)3 * kMmaRows * (dim + kMmaPad) + (size_t)2 * kMmaKeys * (vdim + kMmaPad)) * sizeof(__nv_bfloat16);
+        // prompt-sized batches: 64 rows x 32 keys per stage, four CTAs (16 warps) per SM; decode steps: 64 x 64, fewer barriers per key
+        const int keys = rows == 128 ? 32 : 64;
+        const int trows = 64;
+        const size_t smem = (((size_t)trows + 2 * keys) * (dim + kMmaPad) + (size_t)2 * keys * (vdim + kMmaPad)) * sizeof(__nv_bfloat16);
         using B = __nv_bfloat16;
-#define MMA_LAUNCH(DK, DV)                                                                                                                                         \
+#define MMA_LAUNCH(DK, DV, ROWS, KEYS)                                                                                                                             \
     do {                                                                                                                                                           \
-        GRANT_SMEM((sigmoid_attn_mma_kernel<DK, DV>), smem);                                                                                                       \
-        sigmoid_attn_mma_kernel<DK, DV><<<grid, 128, smem, (cudaStream_t)stream>>>((const B*)q, heads, kv_heads, dim, vdim, scale, bias, n_bias, head_bias, pos, slot, seqs,   \
-                                                                                   seqs_stride, n_seqs, RH, page_table, max_pages, page_size, (const B*)cache, (const B*)gate, \
-                                                                                   gate_stride, (B*)out, splits > 1 ? workspace : nullptr, n_tokens);                        \
+        GRANT_SMEM((sigmoid_attn_mma_kernel<DK, DV, ROWS, KEYS>), smem);                                                                                           \
+        sigmoid_attn_mma_kernel<DK, DV, ROWS, KEYS><<<grid, ROWS * 2, smem, (cudaStream_t)stream>>>((const B*)q, heads, kv_heads, dim, vdim, scale, bias, n_bias, head_bias,  \
+                                                                                                    pos, slot, seqs, seqs_stride, n_seqs, RH, page_table, max_pages,          \
+                                                                                                    page_size, (const B*)cache, (const B*)gate, gate_stride, (B*)out,          \
+                                                                                                    splits > 1 ? workspace : nullptr, n_tokens);                              \
     } while (0)
-        if (dim <= 64 && vdim <= 64) MMA_LAUNCH(4, 4);
-        else MMA_LAUNCH(8, 8);
+        if (dim <= 64 && vdim <= 64) { if (keys == 32) MMA_LAUNCH(4, 4, 64, 32); else MMA_LAUNCH(4, 4, 64, 64); }
+        else { if (keys == 32) MMA_LAUNCH(8, 8, 64, 32); else MMA_LAUNCH(8, 8, 64, 64); }
 #undef MMA_LAUNCH
         KTB_LAUNCH_CHECK();
         if (splits > 1) {
