@@ -435,8 +435,8 @@ int ktb200_sigmoid_bias_attn(const void* q, int heads, int kv_heads, int dim, in
 int ktb200_sigmoid_bias_attn_uses_tensor_cores(int heads, int kv_heads, int dim, int vdim, int dtype);
 int ktb200_sigmoid_bias_attn_tiles(int heads, int kv_heads, int n_tokens, int n_seqs);
 int ktb200_gla_scan(const void* proj, long proj_stride, int q_off, int k_off, int v_off, const void* z, long z_stride, const void* z_bias,
-                    float tau, int heads, int dim, int vdim, const int* seqs, int seqs_stride, int n_seqs, float* state, float* o_out,
-                    int dtype, void* stream);
+                    float tau, int heads, int dim, int vdim, const int* seqs, int seqs_stride, int n_seqs, int n_tokens, float* state,
+                    float* o_out, int dtype, void* stream);
 int ktb200_gla_out(const float* o, const void* norm_w, float eps, const void* gate, long gate_stride, void* out, int n_tokens, int heads,
                    int vdim, int dtype, void* stream);
 int ktb200_xielu(const void* z, void* out, const float* pq, long n, int dtype, void* stream);

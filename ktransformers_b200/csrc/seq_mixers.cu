@@ -399,8 +399,8 @@ __global__ void sigmoid_attn_merge_kernel(const float* __restrict__ partial, int
 constexpr int kGlaChunk = 16;
 constexpr int kGlaWarps = 8;
 constexpr int kGlaRows = 32;         // key channels per thread: dim <= 256
-template <typename T>
-__global__ void __launch_bounds__(256) gla_scan_kernel(const T* __restrict__ proj, long proj_stride, int q_off, int k_off, int v_off, const T* __restrict__ z, long z_stride,
+template <typename T, bool AHEAD>
+__global__ void __launch_bounds__(256, AHEAD ? 2 : 3) gla_scan_kernel(const T* __restrict__ proj, long proj_stride, int q_off, int k_off, int v_off, const T* __restrict__ z, long z_stride,
                                                        const T* __restrict__ z_bias, float inv_tau, float q_scale, int H, int d, int dv, const int* __restrict__ seqs,
                                                        int seqs_stride, float* __restrict__ state, float* __restrict__ o_out) {
     extern __shared__ __align__(16) float sm[];
@@ -421,22 +421,53 @@ __global__ void __launch_bounds__(256) gla_scan_kernel(const T* __restrict__ pro
         const int i = warp * rpt + r;
         S[r] = (rd >= 0 && r < rpt && i < d && col < dv) ? state[rd * srow + ((long)h * d + i) * dv + col] : 0.f;
     }
+    // the next chunk's inputs are fetched into registers while the current chunk runs, and turned into decays and staged afterwards
+    constexpr int E = kGlaChunk * kGlaRows * kGlaWarps / 256;      // staged values per thread and array, at most
+    float rq[E], rk[E], rz[E], rv[2];
+    auto fetch = [&](int t0) {
+        const int nt = min(kGlaChunk, len - t0);
+#pragma unroll
+        for (int e = 0; e < E; e++) {
+            const int i = threadIdx.x + e * 256;
+            rq[e] = rk[e] = rz[e] = 0.f;
+            if (i < nt * dp) {
+                const int tt = i / dp, c = i - tt * dp;
+                const long row = (long)(start + t0 + tt);
+                if (c < d) {
+                    rq[e] = to_f(proj[row * proj_stride + q_off + h * d + c]);
+                    rk[e] = to_f(proj[row * proj_stride + k_off + h * d + c]);
+                    rz[e] = to_f(z[row * z_stride + h * d + c]) + to_f(z_bias[h * d + c]);
+                }
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            const int i = threadIdx.x + e * 256, c = c0 + (i & 31);
+            rv[e] = (i < nt * 32 && c < dv) ? to_f(proj[(long)(start + t0 + (i >> 5)) * proj_stride + v_off + h * dv + c]) : 0.f;
+        }
+    };
+    if (AHEAD && len > 0) fetch(0);
     for (int t0 = 0; t0 < len; t0 += kGlaChunk) {
         const int nt = min(kGlaChunk, len - t0);
+        if (!AHEAD) fetch(t0);      // decode steps: one token per sequence, nothing to run ahead of
         __syncthreads();
-        for (int i = threadIdx.x; i < nt * dp; i += blockDim.x) {
-            const int tt = i / dp, c = i - tt * dp;
-            const long row = (long)(start + t0 + tt);
-            const bool in = c < d;
-            qs[i] = in ? to_f(proj[row * proj_stride + q_off + h * d + c]) * q_scale : 0.f;
-            ks[i] = in ? to_f(proj[row * proj_stride + k_off + h * d + c]) : 0.f;
-            as[i] = in ? expf(log_sigmoid_f(to_f(z[row * z_stride + h * d + c]) + to_f(z_bias[h * d + c])) * inv_tau) : 0.f;
+#pragma unroll
+        for (int e = 0; e < E; e++) {
+            const int i = threadIdx.x + e * 256;
+            if (i < nt * dp) {
+                const int c = i % dp;
+                qs[i] = rq[e] * q_scale;
+                ks[i] = rk[e];
+                as[i] = c < d ? expf(log_sigmoid_f(rz[e]) * inv_tau) : 0.f;
+            }
         }
-        for (int i = threadIdx.x; i < nt * 32; i += blockDim.x) {
-            const int tt = i >> 5, c = c0 + (i & 31);
-            vs[i] = c < dv ? to_f(proj[(long)(start + t0 + tt) * proj_stride + v_off + h * dv + c]) : 0.f;
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            const int i = threadIdx.x + e * 256;
+            if (i < nt * 32) vs[i] = rv[e];
         }
         __syncthreads();
+        if (AHEAD && t0 + kGlaChunk < len) fetch(t0 + kGlaChunk);
         for (int tt = 0; tt < nt; tt++) {
             const float v = vs[tt * 32 + lane];
             const float4* qr = reinterpret_cast<const float4*>(qs + tt * dp + warp * rpt);
@@ -636,7 +667,7 @@ extern "C" int ktb200_sigmoid_bias_attn(const void* q, int heads, int kv_heads, 
 }
 
 extern "C" int ktb200_gla_scan(const void* proj, long proj_stride, int q_off, int k_off, int v_off, const void* z, long z_stride, const void* z_bias, float tau, int heads,
-                               int dim, int vdim, const int* seqs, int seqs_stride, int n_seqs, float* state, float* o_out, int dtype, void* stream) {
+                               int dim, int vdim, const int* seqs, int seqs_stride, int n_seqs, int n_tokens, float* state, float* o_out, int dtype, void* stream) {
     if (!proj || !z || !z_bias || !seqs || !state || !o_out || heads <= 0 || dim <= 0 || dim > kGlaWarps * kGlaRows || vdim <= 0 || !(tau > 0.f)) {
         set_error("gla_scan: bad argument (dim <= %d)", kGlaWarps * kGlaRows);
         return KTB200_EINVAL;
@@ -644,12 +675,16 @@ extern "C" int ktb200_gla_scan(const void* proj, long proj_stride, int q_off, in
     if (n_seqs <= 0) return KTB200_OK;
     const int dp = ((((dim + kGlaWarps - 1) / kGlaWarps) + 3) & ~3) * kGlaWarps;      // key channels padded to whole float4 per warp
     const size_t smem = ((size_t)3 * kGlaChunk * dp + kGlaChunk * 32 + (size_t)kGlaChunk * kGlaWarps * 32) * sizeof(float);
-    SEQ_DISPATCH(dtype, {
-        GRANT_SMEM(gla_scan_kernel<T>, smem);
-        gla_scan_kernel<T><<<dim3(n_seqs, heads, (vdim + 31) / 32), kGlaWarps * 32, smem, (cudaStream_t)stream>>>(
-            (const T*)proj, proj_stride, q_off, k_off, v_off, (const T*)z, z_stride, (const T*)z_bias, 1.0f / tau, 1.0f / sqrtf((float)dim), heads, dim, vdim, seqs, seqs_stride,
-            state, o_out);
-    });
+#define GLA_LAUNCH(AHEAD)                                                                                                                                         \
+    SEQ_DISPATCH(dtype, {                                                                                                                                         \
+        GRANT_SMEM((gla_scan_kernel<T, AHEAD>), smem);                                                                                                            \
+        gla_scan_kernel<T, AHEAD><<<dim3(n_seqs, heads, (vdim + 31) / 32), kGlaWarps * 32, smem, (cudaStream_t)stream>>>(                                         \
+            (const T*)proj, proj_stride, q_off, k_off, v_off, (const T*)z, z_stride, (const T*)z_bias, 1.0f / tau, 1.0f / sqrtf((float)dim), heads, dim, vdim, seqs, \
+            seqs_stride, state, o_out);                                                                                                                           \
+    })
+    if (n_tokens > n_seqs) GLA_LAUNCH(true);      // some portion has several tokens: fetch a chunk ahead
+    else GLA_LAUNCH(false);
+#undef GLA_LAUNCH
     KTB_LAUNCH_CHECK();
     return KTB200_OK;
 }

@@ -127,7 +127,7 @@ SEQ_SYMBOLS = {
     "ktb200_sigmoid_bias_attn": (_I, [_VP, _I, _I, _I, _I, _F, _VP, _I, _VP, _VP, _VP, _VP, _I, _I, _VP, _I, _I, _VP, _VP, _L, _VP, _I, _I, _VP, _I, _I, _VP]),
     "ktb200_sigmoid_bias_attn_uses_tensor_cores": (_I, [_I, _I, _I, _I, _I]),
     "ktb200_sigmoid_bias_attn_tiles": (_I, [_I, _I, _I, _I]),
-    "ktb200_gla_scan": (_I, [_VP, _L, _I, _I, _I, _VP, _L, _VP, _F, _I, _I, _I, _VP, _I, _I, _VP, _VP, _I, _VP]),
+    "ktb200_gla_scan": (_I, [_VP, _L, _I, _I, _I, _VP, _L, _VP, _F, _I, _I, _I, _VP, _I, _I, _I, _VP, _VP, _I, _VP]),
     "ktb200_gla_out": (_I, [_VP, _VP, _F, _VP, _L, _VP, _I, _I, _I, _I, _VP]),
     "ktb200_xielu": (_I, [_VP, _VP, _VP, _L, _I, _VP]),
 }

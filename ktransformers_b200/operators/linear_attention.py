@@ -62,7 +62,7 @@ class KGatedLinearAttention(nn.Module):
         z = torch.nn.functional.linear(proj[:, self.a1_off:self.a1_off + self.rank], self.a2)
         o = torch.empty((T, self.n_v), dtype=torch.float32, device=dev)
         native.check_seq(lib.ktb200_gla_scan(proj.data_ptr(), self.n_in, 0, self.n_qk, 2 * self.n_qk, z.data_ptr(), self.n_qk, self.a2_b.data_ptr(), float(s.tau), s.heads,
-                                             s.dim, s.vdim, batch.seqs.data_ptr(), batch.seqs.stride(0), batch.n_seqs, cache.state[cache_idx].data_ptr(), o.data_ptr(),
+                                             s.dim, s.vdim, batch.seqs.data_ptr(), batch.seqs.stride(0), batch.n_seqs, T, cache.state[cache_idx].data_ptr(), o.data_ptr(),
                                              code, st))
         og = torch.empty((T, self.n_v), dtype=dt, device=dev)
         native.check_seq(lib.ktb200_gla_out(o.data_ptr(), self.norm.data_ptr(), float(self.eps), proj[:, 2 * self.n_qk + self.n_v:].data_ptr(), self.n_in, og.data_ptr(), T,

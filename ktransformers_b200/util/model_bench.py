@@ -368,7 +368,7 @@ def mabidra_kernel_leg(flush, peak_gbs, peak_tflops):
         state, o = torch.zeros(2 * B, GH * gd * gdv, device=dev), torch.empty(B * T, GH * gdv, device=dev)
         seqs = torch.tensor([[i * T for i in range(B)], [T] * B, [2 * i for i in range(B)], [2 * i + 1 for i in range(B)]], dtype=torch.int32, device=dev)
         fn = lambda: native.check_seq(seq.ktb200_gla_scan(proj.data_ptr(), n_in, 0, GH * gd, 2 * GH * gd, z.data_ptr(), GH * gd, zb.data_ptr(), 16.0, GH, gd, gdv, seqs.data_ptr(), B, B,
-                                                          state.data_ptr(), o.data_ptr(), 30, S()))
+                                                          B * T, state.data_ptr(), o.data_ptr(), 30, S()))
         ms = timed(fn, flush, iters=5 if T > 1 else 10)
         if T == 1:
             row("gla_scan_kernel", f"decode B={B} heads={GH} dim={gd} vdim={gdv}", ms, nbytes=B * GH * gd * gdv * 8,
