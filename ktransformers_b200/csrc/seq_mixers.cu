@@ -116,7 +116,7 @@ template <typename T>
 __global__ void __launch_bounds__(256) sigmoid_attn_kernel(const T* __restrict__ q, int H, int G, int d, int dv, float scale, const float* __restrict__ bias, int n_bias,
                                                            const float* __restrict__ pb, const int* __restrict__ pos, const int* __restrict__ slot,
                                                            const int* __restrict__ page_table, int max_pages, int page_size, const T* __restrict__ cache,
-                                                           const T* __restrict__ gate, long gate_stride, T* __restrict__ out, float* __restrict__ partial, int n_tokens) {
+                                                           const T* __restrict__ gate, long gate_stride, T* __restrict__ out, float* __restrict__ partial, int n_tokens, int stage_bias) {
     extern __shared__ __align__(16) float sm[];
     const int HB = blockDim.x >> 5, R = H / G, hblocks = (R + HB - 1) / HB;
     const int g = blockIdx.y / hblocks, hb = blockIdx.y % hblocks;
@@ -139,7 +139,8 @@ __global__ void __launch_bounds__(256) sigmoid_attn_kernel(const T* __restrict__
     if (k_lo < k_hi) {
         if (live) {
             for (int i = lane; i < d; i += 32) qs[warp * d + i] = to_f(q[(t * H + h) * d + i]) * scale;
-            for (int i = lane; i < n_bias; i += 32) bs[warp * n_bias + i] = bias[(long)h * n_bias + i] + pb[h];
+            if (stage_bias)      // a head's bias by distance, when the tables fit shared memory; read from global memory otherwise
+                for (int i = lane; i < n_bias; i += 32) bs[warp * n_bias + i] = bias[(long)h * n_bias + i] + pb[h];
         }
         const int* pt = page_table + (long)slot[t] * max_pages;
         const long cw = (long)G * (d + dv);
@@ -163,7 +164,8 @@ __global__ void __launch_bounds__(256) sigmoid_attn_kernel(const T* __restrict__
                     const float* qr = qs + warp * d;
                     for (int i = 0; i < d; i++) s = fmaf(qr[i], kr[i], s);
                     const int dist = p - (j0 + lane);
-                    w = sigmoid_f(s + bs[warp * n_bias + min(dist, n_bias - 1)]);
+                    const int bi = min(dist, n_bias - 1);
+                    w = sigmoid_f(s + (stage_bias ? bs[warp * n_bias + bi] : bias[(long)h * n_bias + bi] + pb[h]));
                 }
                 for (int j = 0; j < nk; j++) {
                     const float wj = __shfl_sync(0xffffffffu, w, j);
@@ -649,13 +651,15 @@ extern "C" int ktb200_sigmoid_bias_attn(const void* q, int heads, int kv_heads, 
         return KTB200_OK;
     }
     const int R = heads / kv_heads, HB = R < 8 ? R : 8, hblocks = (R + HB - 1) / HB;
-    const size_t smem = ((size_t)HB * dim + (size_t)kAttnTile * (dim + 1) + (size_t)kAttnTile * vdim + (size_t)HB * n_bias) * sizeof(float);
+    const size_t tiles = ((size_t)HB * dim + (size_t)kAttnTile * (dim + 1) + (size_t)kAttnTile * vdim) * sizeof(float);
+    const int stage_bias = tiles + (size_t)HB * n_bias * sizeof(float) <= 96 * 1024;
+    const size_t smem = tiles + (stage_bias ? (size_t)HB * n_bias * sizeof(float) : 0);
     if (smem > 200 * 1024) { set_error("sigmoid_bias_attn: head too wide for shared memory"); return KTB200_EINVAL; }
     SEQ_DISPATCH(dtype, {
         GRANT_SMEM(sigmoid_attn_kernel<T>, smem);
         sigmoid_attn_kernel<T><<<dim3(n_tokens, kv_heads * hblocks, splits), HB * 32, smem, (cudaStream_t)stream>>>(
             (const T*)q, heads, kv_heads, dim, vdim, scale, bias, n_bias, head_bias, pos, slot, page_table, max_pages, page_size, (const T*)cache, (const T*)gate, gate_stride,
-            (T*)out, splits > 1 ? workspace : nullptr, n_tokens);
+            (T*)out, splits > 1 ? workspace : nullptr, n_tokens, stage_bias);
         KTB_LAUNCH_CHECK();
         if (splits > 1) {
             sigmoid_attn_merge_kernel<T><<<grid_for((long)n_tokens * heads * vdim, 256), 256, 0, (cudaStream_t)stream>>>(workspace, splits, (const T*)gate, gate_stride, (T*)out,

@@ -321,6 +321,16 @@ def test_tensor_core_attention_far_value_and_split_edges():
         assert rel(got, want) < 4e-2 and rel(got[690:], want[690:]) < 4e-2 and rel(got, simple) < 1.5e-2
 
 
+@gpu
+def test_bias_table_too_long_for_shared_memory():
+    """a table that reaches 5000 tokens is read from global memory by the CUDA-core kernel; the value that stands out sits inside
+    and outside the logarithmic part"""
+    desc = U.attn(heads=8, kv_heads=1, dim=8, vdim=8, rows=16, bias_max=5000)
+    for dtype, tol in ((torch.float32, 2e-5), (torch.bfloat16, 4e-2)):
+        got, want = mixer_alone(desc, dtype, 300, 64, [290] + [1] * 10, big_at=5)
+        assert rel(got, want) < tol
+
+
 GLA_SHAPES = [U.gla(), U.gla(heads=2, dim=17, vdim=33, tau=9.0, rank=3), U.gla(heads=1, dim=64, vdim=64, tau=16.0, rank=8), U.gla(heads=5, dim=3, vdim=1, tau=1.0, rank=1),
               U.gla(heads=2, dim=130, vdim=70, tau=30.0, rank=4)]
 
