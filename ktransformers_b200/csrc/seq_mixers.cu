@@ -26,6 +26,8 @@ __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log
 // log(sigmoid(x)) without overflow on either side
 __device__ __forceinline__ float log_sigmoid_f(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
+__device__ __forceinline__ void prefetch_l2_line(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
 // ------------------------------------------------------------------------------------------------ sandwich norm
 // One CTA per token.  Shared memory: red[32] | row[D] (the new residual row, when it fits).
 template <typename T>
@@ -38,6 +40,60 @@ __global__ void __launch_bounds__(256) sandwich_norm_kernel(const float* __restr
     const long t = blockIdx.x;
     const int tid = threadIdx.x, gs = D / groups;
     const bool vec = (gs & 3) == 0;
+    const int lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
+    if (stash && nw % groups == 0 && gs % (4 * (nw / groups)) == 0) {
+        // every warp owns one of nw equal chunks of the row (a group = nw / groups consecutive chunks): all groups advance together,
+        // three barriers per row, 16-byte accesses; what the later passes read is asked into L2 while the first pass runs
+        const int per = nw / groups, chunk = gs / per, lo = warp * chunk, g0 = (warp / per) * per;
+        for (int i = lane * 32; i < chunk; i += 1024) {
+            if (x_in) prefetch_l2_line(x_in + t * D + lo + i);
+            if (row_add) prefetch_l2_line(row_add + lo + i);
+        }
+        for (int i = lane * (128 / (int)sizeof(T)); i < chunk; i += 32 * (128 / (int)sizeof(T))) {
+            if (w_post) prefetch_l2_line(w_post + lo + i);
+            if (w_pre) prefetch_l2_line(w_pre + lo + i);
+        }
+        float s = 0.f;
+        for (int i = lane * 4; i < chunk; i += 128) {
+            const float4 v = load4_hidden(y, t * D + lo + i, y_type);
+            store4(row + lo + i, v);
+            s += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+        }
+        float inv = 1.f;
+        if (w_post) {
+            s = warp_sum(s);
+            if (lane == 0) red[warp] = s;
+            __syncthreads();
+            float a = 0.f;
+            for (int k = 0; k < per; k++) a += red[g0 + k];
+            inv = 1.0f / sqrtf(a / (float)gs + eps);
+        }
+        float s2 = 0.f;
+        for (int i = lane * 4; i < chunk; i += 128) {
+            float4 v = load4(row + lo + i);
+            if (w_post) { const float4 w = load4(w_post + lo + i); v.x = v.x * inv * w.x; v.y = v.y * inv * w.y; v.z = v.z * inv * w.z; v.w = v.w * inv * w.w; }
+            if (x_in) { const float4 u = load4(x_in + t * D + lo + i); v.x = u.x + v.x; v.y = u.y + v.y; v.z = u.z + v.z; v.w = u.w + v.w; }
+            if (row_add) { const float4 u = load4(row_add + lo + i); v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w; }
+            if (x_out) store4(x_out + t * D + lo + i, v);
+            store4(row + lo + i, v);
+            s2 += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+        }
+        if (w_pre) {
+            s2 = warp_sum(s2);
+            if (lane == 0) red[16 + warp] = s2;
+            __syncthreads();
+            float a = 0.f;
+            for (int k = 0; k < per; k++) a += red[16 + g0 + k];
+            const float inv2 = 1.0f / sqrtf(a / (float)gs + eps);
+            for (int i = lane * 4; i < chunk; i += 128) {
+                float4 v = load4(row + lo + i);
+                const float4 w = load4(w_pre + lo + i);
+                v.x = v.x * inv2 * w.x; v.y = v.y * inv2 * w.y; v.z = v.z * inv2 * w.z; v.w = v.w * inv2 * w.w;
+                store4(h_out + t * D + lo + i, v);
+            }
+        }
+        return;
+    }
     for (int g = 0; g < groups; g++) {
         const int lo = g * gs;
         float inv = 1.f;
