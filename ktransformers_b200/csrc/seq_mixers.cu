@@ -337,7 +337,7 @@ __global__ void __launch_bounds__(ROWS * 2, (ROWS == 64 && KEYS == 32) ? 4 : 1) 
             cp_async16(Qs + r * ldk + c * 8, ok ? q + ((long)(tok0 + tk) * H + h0 + r % RH) * d + c * 8 : q, ok);
         }
         // TPR = 2 or 4 neighbouring threads copy key row r of a tile: one page-table lookup per thread and tile, made a tile ahead
-        // of its copies, and 16-byte chunks dealt round the TPR threads (together they fill whole 32-byte sectors)
+        // of its copies, and 16-byte chunks dealt out over the TPR threads (together they fill whole 32-byte sectors)
         constexpr int TPR = ROWS * 2 / KEYS;
         const int lrow = tid / TPR, lpar = tid % TPR;
         auto row_base = [&](int kp) -> long {
