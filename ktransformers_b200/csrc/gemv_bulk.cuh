@@ -43,18 +43,25 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
                  "l"(src), "r"(bytes), "r"(bar)
                  : "memory");
 }
+// bounded wait for a phase of an mbarrier: gives up after kMbarWaitLimit polls (seconds), counts that in g_mbar_wait_gave_up and
+// returns, so that a copy that never completes ends the kernel (with wrong results) instead of holding the GPU
+constexpr uint32_t kMbarWaitLimit = 1u << 24;
+static __device__ unsigned int g_mbar_wait_gave_up;
 __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity) {
-    asm volatile(
-        "{\n"
-        ".reg .pred P1;\n"
-        "LAB_WAIT:\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 P1, [%0], %1;\n"
-        "@P1 bra DONE;\n"
-        "bra LAB_WAIT;\n"
-        "DONE:\n"
-        "}" ::"r"(bar),
-        "r"(parity)
-        : "memory");
+    for (uint32_t it = 0; it < kMbarWaitLimit; it++) {
+        uint32_t done;
+        asm volatile(
+            "{\n"
+            ".reg .pred P1;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, P1;\n"
+            "}"
+            : "=r"(done)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (done) return;
+    }
+    atomicAdd(&g_mbar_wait_gave_up, 1u);
 }
 
 // ---------------------------------------------------------------------------------------------------------------

@@ -23,18 +23,28 @@ __device__ __forceinline__ void bar_arrive(uint32_t bar) {
 __device__ __forceinline__ void bar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-// blocks until the phase with the given parity has completed (a fresh barrier passes parity 1 at once)
-__device__ __forceinline__ void bar_wait(uint32_t bar, uint32_t parity) {
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "WAIT_LOOP:\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%0], %1;\n"
-        "@p bra WAIT_DONE;\n"
-        "bra WAIT_LOOP;\n"
-        "WAIT_DONE:\n"
-        "}\n" ::"r"(bar), "r"(parity)
-        : "memory");
+// Waits until the phase with the given parity has completed (a fresh barrier passes parity 1 at once).  The wait is bounded:
+// after kBarWaitLimit polls (each poll suspends the thread for a hardware-defined while; seconds in all) it gives up, counts the
+// event in g_bar_wait_gave_up and returns false, so a kernel whose copy or MMA never arrives still ends (with wrong results)
+// instead of occupying the GPU for good.
+constexpr uint32_t kBarWaitLimit = 1u << 24;
+static __device__ unsigned int g_bar_wait_gave_up;
+__device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t it = 0; it < kBarWaitLimit; it++) {
+        uint32_t done;
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(done)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    atomicAdd(&g_bar_wait_gave_up, 1u);
+    return false;
 }
 // generic-proxy writes to shared memory (st.shared) -> visible to the async proxy (TMA, tcgen05.mma operand reads)
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
