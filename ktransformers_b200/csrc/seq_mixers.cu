@@ -246,9 +246,9 @@ __global__ void __launch_bounds__(256) sigmoid_attn_kernel(const T* __restrict__
 }
 
 // ------------------------------------------------------------------------------------------------ sigmoid attention, tensor cores (bf16)
-// A CTA of ROWS / 16 warps owns a tile of ROWS (64 or 128) rows = (token, query head) pairs of ONE sequence portion and ONE key/value
-// head: `RH` query heads of the group for each of ROWS / RH consecutive tokens; KEYS = 64 or 32 keys per ring stage (prompt portions fill the rows with tokens, decode steps with the
-// group's heads).  Keys run in tiles of 64 through a two-stage cp.async ring of [k | v] rows gathered through the page table;
+// A CTA of ROWS / 16 warps owns a tile of ROWS (64 as launched) rows = (token, query head) pairs of ONE sequence portion and ONE
+// key/value head: `RH` query heads of the group for each of ROWS / RH consecutive tokens; KEYS (32 as launched) keys per ring stage (prompt portions fill the rows with tokens, decode steps with the
+// group's heads).  Keys run in tiles of KEYS through a two-stage cp.async ring of [k | v] rows gathered through the page table;
 // S = Q K^T and O += P V are m16n8k16 bf16 MMAs with fp32 accumulators; the scores are scaled, biased and pushed through the
 // sigmoid in fp32 registers and handed to the second product as bf16.  No running maximum and no rescaling: the weights are
 // not normalised.  grid (tile bound, G * head blocks, splits); tiles are found from the per-sequence rows `seqs`.
@@ -661,12 +661,8 @@ static int mma_heads_per_tile(int group) {
 extern "C" int ktb200_sigmoid_bias_attn_uses_tensor_cores(int heads, int kv_heads, int dim, int vdim, int dtype) {
     return dtype == KTB200_TYPE_BF16 && kv_heads > 0 && heads % kv_heads == 0 && dim % 16 == 0 && vdim % 16 == 0 && dim <= 128 && vdim <= 128;
 }
-// whether the batch is prompt-sized: the sequence portions bring 128 or more (token, head) rows on average
-static int mma_rows_per_tile(int group, int n_tokens, int n_seqs) {
-    return (long)n_tokens * mma_heads_per_tile(group) >= (long)128 * (n_seqs > 0 ? n_seqs : 1) ? 128 : 64;
-}
 extern "C" int ktb200_sigmoid_bias_attn_tiles(int heads, int kv_heads, int n_tokens, int n_seqs) {
-    return n_seqs + n_tokens / (64 / mma_heads_per_tile(heads / kv_heads));
+    return n_seqs + n_tokens / (kMmaRows / mma_heads_per_tile(heads / kv_heads));
 }
 
 extern "C" int ktb200_sigmoid_bias_attn(const void* q, int heads, int kv_heads, int dim, int vdim, float scale, const float* bias, int n_bias, const float* head_bias,
@@ -680,23 +676,21 @@ extern "C" int ktb200_sigmoid_bias_attn(const void* q, int heads, int kv_heads, 
     }
     if (n_tokens <= 0) return KTB200_OK;
     if (allow_tensor_cores && seqs && n_seqs > 0 && ktb200_sigmoid_bias_attn_uses_tensor_cores(heads, kv_heads, dim, vdim, dtype)) {
-        const int RH = mma_heads_per_tile(heads / kv_heads), rows = mma_rows_per_tile(heads / kv_heads, n_tokens, n_seqs);
+        const int RH = mma_heads_per_tile(heads / kv_heads);
         const dim3 grid(ktb200_sigmoid_bias_attn_tiles(heads, kv_heads, n_tokens, n_seqs), kv_heads * (heads / kv_heads / RH), splits);
-        // prompt-sized batches: 64 rows x 32 keys per stage, four CTAs (16 warps) per SM; decode steps: 64 x 64, fewer barriers per key
-        const int keys = rows == 128 ? 32 : 64;
-        const int trows = 64;
-        const size_t smem = (((size_t)trows + 2 * keys) * (dim + kMmaPad) + (size_t)2 * keys * (vdim + kMmaPad)) * sizeof(__nv_bfloat16);
+        // 64 rows x 32 keys per ring stage: 128 registers and ~52 KB, four CTAs (16 warps) per SM, for prompt portions and decode steps alike
+        const size_t smem = (((size_t)kMmaRows + 2 * 32) * (dim + kMmaPad) + (size_t)2 * 32 * (vdim + kMmaPad)) * sizeof(__nv_bfloat16);
         using B = __nv_bfloat16;
-#define MMA_LAUNCH(DK, DV, ROWS, KEYS)                                                                                                                             \
+#define MMA_LAUNCH(DK, DV)                                                                                                                                         \
     do {                                                                                                                                                           \
-        GRANT_SMEM((sigmoid_attn_mma_kernel<DK, DV, ROWS, KEYS>), smem);                                                                                           \
-        sigmoid_attn_mma_kernel<DK, DV, ROWS, KEYS><<<grid, ROWS * 2, smem, (cudaStream_t)stream>>>((const B*)q, heads, kv_heads, dim, vdim, scale, bias, n_bias, head_bias,  \
-                                                                                                    pos, slot, seqs, seqs_stride, n_seqs, RH, page_table, max_pages,          \
-                                                                                                    page_size, (const B*)cache, (const B*)gate, gate_stride, (B*)out,          \
-                                                                                                    splits > 1 ? workspace : nullptr, n_tokens);                              \
+        GRANT_SMEM((sigmoid_attn_mma_kernel<DK, DV, kMmaRows, 32>), smem);                                                                                         \
+        sigmoid_attn_mma_kernel<DK, DV, kMmaRows, 32><<<grid, kMmaRows * 2, smem, (cudaStream_t)stream>>>((const B*)q, heads, kv_heads, dim, vdim, scale, bias, n_bias,      \
+                                                                                                          head_bias, pos, slot, seqs, seqs_stride, n_seqs, RH, page_table, \
+                                                                                                          max_pages, page_size, (const B*)cache, (const B*)gate,           \
+                                                                                                          gate_stride, (B*)out, splits > 1 ? workspace : nullptr, n_tokens); \
     } while (0)
-        if (dim <= 64 && vdim <= 64) { if (keys == 32) MMA_LAUNCH(4, 4, 64, 32); else MMA_LAUNCH(4, 4, 64, 64); }
-        else { if (keys == 32) MMA_LAUNCH(8, 8, 64, 32); else MMA_LAUNCH(8, 8, 64, 64); }
+        if (dim <= 64 && vdim <= 64) MMA_LAUNCH(4, 4);
+        else MMA_LAUNCH(8, 8);
 #undef MMA_LAUNCH
         KTB_LAUNCH_CHECK();
         if (splits > 1) {

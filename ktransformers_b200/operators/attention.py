@@ -197,6 +197,8 @@ def distance_bias_table(rel: torch.Tensor, bias_max: float) -> torch.Tensor:
     logarithmic up to `bias_max`, constant beyond."""
     B = rel.shape[0]
     half = B // 2
+    if half < 1 or not bias_max > half:
+        raise ValueError(f"a distance bias table of {B} rows needs at least 2 rows and a reach beyond {half} (got {bias_max})")
     buckets, n = [], 0
     while True:
         b = n if n < half else min(B - 1, half + int(math.floor(math.log(n / half) / math.log(bias_max / half) * (B - half))))
@@ -266,6 +268,8 @@ class KSigmoidBiasAttention(torch.nn.Module):
             ctas = n_tokens * s.kv_heads * ((s.heads // s.kv_heads + 7) // 8)
         if ctas >= 148 or max_kv <= 256:
             return 1
+        if tensor_cores:      # four CTAs per SM; parts of 64 keys or more
+            return max(1, min(128, max_kv // 64, 1184 // ctas))
         return max(1, min(64, max_kv // 128, 592 // ctas))
 
     def forward(self, h: torch.Tensor, batch, cache, cache_idx: int) -> torch.Tensor:

@@ -378,6 +378,26 @@ def test_prompt_decode_and_portions_agree_with_the_restatement(tmp_path, dtype, 
 
 
 @gpu
+def test_whole_model_in_bf16_on_tensor_core_head_sizes(tmp_path):
+    """head sizes that are multiples of 16: bf16 attention runs on the tensor-core tiles inside a whole model (a looped span,
+    grouped heads, 150 tokens over three key tiles), whole, in portions and with a decoded tail"""
+    layers = [(U.attn(heads=6, kv_heads=2, dim=32, vdim=48, rows=12, bias_max=40, every=20), U.dense(96)), (U.gla(heads=4, dim=32, vdim=16, tau=6.0), U.moe(ff=32, experts=6, top=2)),
+              (U.attn(heads=4, kv_heads=4, dim=16, vdim=16, rows=6, bias_max=100), U.moe(ff=16, experts=4, top=1))]
+    cfg = U.config(layers, width=64, groups=2, vocab=90, loop=(1, 3, 2))
+    eng, om = serve(tmp_path, cfg, "bfloat16", seed=3, max_tokens=512, max_slots=2, page_size=16)
+    t = toks(150, 90, seed=9)
+    want = oracle_logits(om, t)
+    for k, sizes in enumerate(([150], [70, 3, 2, 40, 1, 34], [130] + [1] * 20)):
+        assert rel_rows(run_steps(eng, cut(("m", k), t, sizes))[("m", k)], want) < BF16_TOL
+
+
+def test_distance_table_refuses_a_reach_inside_the_exact_part():
+    from ktransformers_b200.operators.attention import distance_bias_table
+    with pytest.raises(ValueError):
+        distance_bias_table(torch.zeros(8, 2), 4.0)
+
+
+@gpu
 def test_residual_stream_after_every_layer_run(tmp_path):
     cfg = U.config(MIXED, loop=LOOP)
     eng, om = serve(tmp_path, cfg, "float32", max_tokens=64, max_slots=2, page_size=8)
