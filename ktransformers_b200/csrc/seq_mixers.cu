@@ -389,17 +389,29 @@ __global__ void __launch_bounds__(ROWS * 2, (ROWS == 64 && KEYS == 32) ? 4 : 1) 
                 }
             }
             const bool far = warp_min_pos - (j0 + KEYS - 1) >= n_bias - 1;      // every distance of this warp's rows in this tile reads the table's last entry
+            // and nothing to mask: all 16 rows carry tokens, every key of the tile lies at or before the earliest of them and inside this split
+            const bool plain = far && (warp * 16 + 15) / RH < ntok && j0 + KEYS <= k_hi;
+            if (plain) {
 #pragma unroll
-            for (int n = 0; n < KEYS / 8; n++) {
+                for (int n = 0; n < KEYS / 8; n++) {
+                    S[n][0] = sigmoid_fast(fmaf(S[n][0], scale, farA));
+                    S[n][1] = sigmoid_fast(fmaf(S[n][1], scale, farA));
+                    S[n][2] = sigmoid_fast(fmaf(S[n][2], scale, farB));
+                    S[n][3] = sigmoid_fast(fmaf(S[n][3], scale, farB));
+                }
+            } else {
 #pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    const int key = j0 + n * 8 + 2 * tq + (e & 1);
-                    const bool second = e >= 2;
-                    const int dist = (second ? pB : pA) - key;
-                    const bool ok = (second ? vB : vA) && dist >= 0 && key < k_hi;
-                    float bias_v = second ? farB : farA;
-                    if (!far && ok) bias_v = __ldg((second ? bB : bA) + min(dist, n_bias - 1)) + (second ? pbB : pbA);
-                    S[n][e] = ok ? sigmoid_fast(fmaf(S[n][e], scale, bias_v)) : 0.f;
+                for (int n = 0; n < KEYS / 8; n++) {
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const int key = j0 + n * 8 + 2 * tq + (e & 1);
+                        const bool second = e >= 2;
+                        const int dist = (second ? pB : pA) - key;
+                        const bool ok = (second ? vB : vA) && dist >= 0 && key < k_hi;
+                        float bias_v = second ? farB : farA;
+                        if (!far && ok) bias_v = __ldg((second ? bB : bA) + min(dist, n_bias - 1)) + (second ? pbB : pbA);
+                        S[n][e] = ok ? sigmoid_fast(fmaf(S[n][e], scale, bias_v)) : 0.f;
+                    }
                 }
             }
 #pragma unroll
